@@ -1,0 +1,402 @@
+// KV-cache operations for sm_100a: reshape_and_cache, gather_cached_kv, copy_blocks.
+//
+// All three are pure data movement and bit-exact.  Index math follows
+// rllm/tch-cuda/kernels/vllm/cache_kernels.cu (:168-213 scatter, :301-373 gather,
+// :55-81 block copy); the traversal does not: every global access is a 16-byte vector, the
+// value tile is transposed through shared memory so that runs of consecutive slots are
+// written along block_size as whole 16-byte pieces, and the block copy moves 16 bytes per
+// thread per access with the layer/pair tables optionally passed as kernel arguments.
+#include "common.cuh"
+
+namespace aici {
+
+constexpr int kD = 128;      // head_size
+constexpr int kB = 16;       // block_size (tokens per cache block)
+constexpr int kX = 8;        // 16 bytes of bf16
+constexpr int kTok = 16;     // tokens per CTA
+constexpr int kThreads = 256;
+
+template <bool kSlot64>
+__device__ __forceinline__ int64_t load_slot(const void *slots, int64_t i) {
+  if (kSlot64) return static_cast<const int64_t *>(slots)[i];
+  return static_cast<int64_t>(static_cast<const int32_t *>(slots)[i]);
+}
+
+// One CTA moves kTok consecutive tokens of one kv head.
+//   K: chunk c (8 elements) of token t -> key_cache[blk][h][c][off][0..7]   (16 B vector)
+//   V: element d of token t            -> value_cache[blk][h][d][off]       (2 B, 32 B apart)
+// For V the CTA transposes its [kTok][128] tile in shared memory; a thread then owns one
+// (d, half) pair and writes 8 tokens as one 16-byte store when their slots are consecutive
+// and 8-aligned inside one block (the prefill case), else element by element (decode).
+template <bool kSlot64>
+__global__ void __launch_bounds__(kThreads)
+reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
+                         const __nv_bfloat16 *__restrict__ value,
+                         __nv_bfloat16 *__restrict__ key_cache,
+                         __nv_bfloat16 *__restrict__ value_cache,
+                         const void *__restrict__ slot_mapping, int num_tokens, int num_kv_heads,
+                         int64_t num_slots, int64_t key_stride, int64_t value_stride,
+                         unsigned int *status) {
+  __shared__ int64_t s_slot[kTok];
+  __shared__ __align__(16) __nv_bfloat16 s_v[kD][kTok + 8];  // [d][tok], padded row = 48 B
+  const int t0 = blockIdx.x * kTok;
+  const int h = blockIdx.y;
+  const int tid = threadIdx.x;
+
+  if (tid < kTok) {
+    int64_t slot = -1;
+    if (t0 + tid < num_tokens) {
+      slot = load_slot<kSlot64>(slot_mapping, t0 + tid);
+      if (slot >= num_slots) {
+        set_status(status, AICI_STATUS_BAD_SLOT);
+        slot = -1;
+      }
+    }
+    s_slot[tid] = slot;
+  }
+  __syncthreads();
+
+  // ---- K: thread (c, tok); 16 consecutive threads cover 16 tokens of one chunk ----------
+  {
+    const int c = tid >> 4, tok = tid & 15;
+    const int64_t slot = s_slot[tok];
+    if (slot >= 0) {
+      const int64_t blk = slot / kB, off = slot % kB;
+      const uint4 val = *reinterpret_cast<const uint4 *>(key + (int64_t)(t0 + tok) * key_stride +
+                                                         h * kD + c * kX);
+      __nv_bfloat16 *dst =
+          key_cache + ((blk * num_kv_heads + h) * (kD / kX) + c) * (kB * kX) + off * kX;
+      *reinterpret_cast<uint4 *>(dst) = val;
+    }
+  }
+  // ---- V: stage transposed --------------------------------------------------------------
+  {
+    const int tok = tid >> 4, part = tid & 15;
+    if (s_slot[tok] >= 0) {
+      const uint4 val = *reinterpret_cast<const uint4 *>(
+          value + (int64_t)(t0 + tok) * value_stride + h * kD + part * kX);
+      const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&val);
+#pragma unroll
+      for (int j = 0; j < kX; ++j) s_v[part * kX + j][tok] = e[j];
+    }
+  }
+  __syncthreads();
+  {
+    const int d = tid >> 1, half = tid & 1;
+    const int tb = half * 8;
+    const int64_t s0 = s_slot[tb];
+    bool run = s0 >= 0 && (s0 % 8) == 0;
+#pragma unroll
+    for (int j = 1; j < 8; ++j) run = run && (s_slot[tb + j] == s0 + j);
+    if (run) {
+      const int64_t blk = s0 / kB, off = s0 % kB;
+      __nv_bfloat16 *dst = value_cache + ((blk * num_kv_heads + h) * kD + d) * kB + off;
+      *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(&s_v[d][tb]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int64_t slot = s_slot[tb + j];
+        if (slot >= 0) {
+          const int64_t blk = slot / kB, off = slot % kB;
+          value_cache[((blk * num_kv_heads + h) * kD + d) * kB + off] = s_v[d][tb + j];
+        }
+      }
+    }
+  }
+}
+
+// Inverse traversal: cache -> packed key/value rows.
+__global__ void __launch_bounds__(kThreads)
+gather_cached_kv_kernel(__nv_bfloat16 *__restrict__ key, __nv_bfloat16 *__restrict__ value,
+                        const __nv_bfloat16 *__restrict__ key_cache,
+                        const __nv_bfloat16 *__restrict__ value_cache,
+                        const int32_t *__restrict__ slot_mapping, int num_tokens,
+                        int num_kv_heads, int64_t num_slots, int64_t key_stride,
+                        int64_t value_stride, unsigned int *status) {
+  __shared__ int64_t s_slot[kTok];
+  __shared__ __align__(16) __nv_bfloat16 s_v[kD][kTok + 8];
+  const int t0 = blockIdx.x * kTok;
+  const int h = blockIdx.y;
+  const int tid = threadIdx.x;
+
+  if (tid < kTok) {
+    int64_t slot = -1;
+    if (t0 + tid < num_tokens) {
+      slot = slot_mapping[t0 + tid];
+      if (slot < 0 || slot >= num_slots) {
+        set_status(status, AICI_STATUS_BAD_SLOT);
+        slot = -1;
+      }
+    }
+    s_slot[tid] = slot;
+  }
+  __syncthreads();
+  {
+    const int c = tid >> 4, tok = tid & 15;
+    const int64_t slot = s_slot[tok];
+    if (slot >= 0) {
+      const int64_t blk = slot / kB, off = slot % kB;
+      const __nv_bfloat16 *src =
+          key_cache + ((blk * num_kv_heads + h) * (kD / kX) + c) * (kB * kX) + off * kX;
+      *reinterpret_cast<uint4 *>(key + (int64_t)(t0 + tok) * key_stride + h * kD + c * kX) =
+          *reinterpret_cast<const uint4 *>(src);
+    }
+  }
+  {
+    const int d = tid >> 1, half = tid & 1;
+    const int tb = half * 8;
+    const int64_t s0 = s_slot[tb];
+    bool run = s0 >= 0 && (s0 % 8) == 0;
+#pragma unroll
+    for (int j = 1; j < 8; ++j) run = run && (s_slot[tb + j] == s0 + j);
+    if (run) {
+      const int64_t blk = s0 / kB, off = s0 % kB;
+      *reinterpret_cast<uint4 *>(&s_v[d][tb]) = *reinterpret_cast<const uint4 *>(
+          value_cache + ((blk * num_kv_heads + h) * kD + d) * kB + off);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int64_t slot = s_slot[tb + j];
+        if (slot >= 0) {
+          const int64_t blk = slot / kB, off = slot % kB;
+          s_v[d][tb + j] = value_cache[((blk * num_kv_heads + h) * kD + d) * kB + off];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  {
+    const int tok = tid >> 4, part = tid & 15;
+    if (s_slot[tok] >= 0) {
+      uint4 val;
+      __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&val);
+#pragma unroll
+      for (int j = 0; j < kX; ++j) e[j] = s_v[part * kX + j][tok];
+      *reinterpret_cast<uint4 *>(value + (int64_t)(t0 + tok) * value_stride + h * kD +
+                                 part * kX) = val;
+    }
+  }
+}
+
+// ---- copy_blocks ---------------------------------------------------------------------------
+constexpr int kCopyThreads = 256;
+constexpr int kCopyUnroll = 8;
+
+__device__ __forceinline__ void copy_block_16B(const uint4 *__restrict__ src,
+                                               uint4 *__restrict__ dst, int n_vec) {
+  for (int base = 0; base < n_vec; base += kCopyThreads * kCopyUnroll) {
+    uint4 v[kCopyUnroll];
+#pragma unroll
+    for (int u = 0; u < kCopyUnroll; ++u) {
+      const int i = base + u * kCopyThreads + threadIdx.x;
+      if (i < n_vec) v[u] = src[i];
+    }
+#pragma unroll
+    for (int u = 0; u < kCopyUnroll; ++u) {
+      const int i = base + u * kCopyThreads + threadIdx.x;
+      if (i < n_vec) dst[i] = v[u];
+    }
+  }
+}
+
+// grid (num_pairs, 2 * num_layers): blockIdx.y < num_layers copies a key block, else a value
+// block.  Tables live in device memory (the reference's calling convention).
+__global__ void __launch_bounds__(kCopyThreads)
+copy_blocks_kernel(const int64_t *__restrict__ key_cache_ptrs,
+                   const int64_t *__restrict__ value_cache_ptrs,
+                   const int64_t *__restrict__ block_mapping, int num_layers,
+                   int64_t bytes_per_block, int64_t num_blocks, unsigned int *status) {
+  const int pair = blockIdx.x;
+  const int layer = blockIdx.y % num_layers;
+  const bool is_value = blockIdx.y >= num_layers;
+  const int64_t src = block_mapping[2 * pair], dst = block_mapping[2 * pair + 1];
+  if (src < 0 || dst < 0 || (num_blocks > 0 && (src >= num_blocks || dst >= num_blocks))) {
+    if (threadIdx.x == 0) set_status(status, AICI_STATUS_BAD_BLOCK);
+    return;
+  }
+  if (src == dst) return;
+  char *base = reinterpret_cast<char *>(is_value ? value_cache_ptrs[layer] : key_cache_ptrs[layer]);
+  copy_block_16B(reinterpret_cast<const uint4 *>(base + src * bytes_per_block),
+                 reinterpret_cast<uint4 *>(base + dst * bytes_per_block),
+                 static_cast<int>(bytes_per_block / 16));
+}
+
+// Same copy with the tables passed by value in the kernel-argument buffer (< 4 KB).
+constexpr int kArgLayers = 96;
+constexpr int kArgPairs = 192;
+struct CopyArgs {
+  int64_t key_ptrs[kArgLayers];
+  int64_t value_ptrs[kArgLayers];
+  int32_t src[kArgPairs];
+  int32_t dst[kArgPairs];
+};
+static_assert(sizeof(CopyArgs) <= 3072 + 64, "kernel arguments must stay below 4 KB");
+
+__global__ void __launch_bounds__(kCopyThreads)
+copy_blocks_args_kernel(const __grid_constant__ CopyArgs args, int num_layers,
+                        int64_t bytes_per_block) {
+  const int pair = blockIdx.x;
+  const int layer = blockIdx.y % num_layers;
+  const bool is_value = blockIdx.y >= num_layers;
+  const int64_t src = args.src[pair], dst = args.dst[pair];
+  if (src == dst) return;
+  char *base = reinterpret_cast<char *>(is_value ? args.value_ptrs[layer] : args.key_ptrs[layer]);
+  copy_block_16B(reinterpret_cast<const uint4 *>(base + src * bytes_per_block),
+                 reinterpret_cast<uint4 *>(base + dst * bytes_per_block),
+                 static_cast<int>(bytes_per_block / 16));
+}
+
+static char *check_cache_shape(const char *fn, int num_kv_heads, int head_size, int block_size,
+                               int dtype) {
+  AICI_CHECK(dtype == AICI_DTYPE_BF16, "%s: only bf16 is supported (dtype=%d)", fn, dtype);
+  AICI_CHECK(head_size == kD, "%s: head_size must be 128 (got %d)", fn, head_size);
+  AICI_CHECK(block_size == kB, "%s: block_size must be 16 (got %d)", fn, block_size);
+  AICI_CHECK(num_kv_heads > 0 && num_kv_heads <= 65535, "%s: bad num_kv_heads %d", fn,
+             num_kv_heads);
+  return nullptr;
+}
+
+}  // namespace aici
+
+using namespace aici;
+
+extern "C" char *aici_reshape_and_cache(const void *key, const void *value, void *key_cache,
+                                        void *value_cache, const void *slot_mapping,
+                                        int slot_is_int64, int num_tokens, int num_kv_heads,
+                                        int head_size, int block_size, int64_t num_blocks,
+                                        int64_t key_stride, int64_t value_stride, int dtype,
+                                        aici_stream_t stream) {
+  const char *fn = "aici_reshape_and_cache";
+  if (char *e = check_cache_shape(fn, num_kv_heads, head_size, block_size, dtype)) return e;
+  AICI_CHECK(num_tokens >= 0, "%s: negative num_tokens", fn);
+  if (num_tokens == 0) return nullptr;
+  AICI_CHECK(key && value && key_cache && value_cache && slot_mapping, "%s: NULL pointer", fn);
+  AICI_CHECK(num_blocks > 0, "%s: num_blocks must be positive", fn);
+  AICI_CHECK(key_stride % 8 == 0 && value_stride % 8 == 0 &&
+                 key_stride >= (int64_t)num_kv_heads * head_size &&
+                 value_stride >= (int64_t)num_kv_heads * head_size,
+             "%s: token strides must be multiples of 8 elements and cover one row", fn);
+  AICI_CHECK(((uintptr_t)key | (uintptr_t)value | (uintptr_t)key_cache |
+              (uintptr_t)value_cache) % 16 == 0,
+             "%s: tensors must be 16-byte aligned", fn);
+  unsigned int *st = status_ptr();
+  AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
+  dim3 grid((num_tokens + kTok - 1) / kTok, num_kv_heads);
+  const int64_t num_slots = num_blocks * kB;
+  auto k = static_cast<const __nv_bfloat16 *>(key);
+  auto v = static_cast<const __nv_bfloat16 *>(value);
+  auto kc = static_cast<__nv_bfloat16 *>(key_cache);
+  auto vc = static_cast<__nv_bfloat16 *>(value_cache);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (slot_is_int64)
+    reshape_and_cache_kernel<true><<<grid, kThreads, 0, s>>>(
+        k, v, kc, vc, slot_mapping, num_tokens, num_kv_heads, num_slots, key_stride, value_stride, st);
+  else
+    reshape_and_cache_kernel<false><<<grid, kThreads, 0, s>>>(
+        k, v, kc, vc, slot_mapping, num_tokens, num_kv_heads, num_slots, key_stride, value_stride, st);
+  AICI_CUDA(cudaGetLastError());
+  return nullptr;
+}
+
+extern "C" char *aici_gather_cached_kv(void *key, void *value, const void *key_cache,
+                                       const void *value_cache, const int32_t *slot_mapping,
+                                       int num_tokens, int num_kv_heads, int head_size,
+                                       int block_size, int64_t num_blocks, int64_t key_stride,
+                                       int64_t value_stride, int dtype, aici_stream_t stream) {
+  const char *fn = "aici_gather_cached_kv";
+  if (char *e = check_cache_shape(fn, num_kv_heads, head_size, block_size, dtype)) return e;
+  AICI_CHECK(num_tokens >= 0, "%s: negative num_tokens", fn);
+  if (num_tokens == 0) return nullptr;
+  AICI_CHECK(key && value && key_cache && value_cache && slot_mapping, "%s: NULL pointer", fn);
+  AICI_CHECK(num_blocks > 0, "%s: num_blocks must be positive", fn);
+  AICI_CHECK(key_stride % 8 == 0 && value_stride % 8 == 0 &&
+                 key_stride >= (int64_t)num_kv_heads * head_size &&
+                 value_stride >= (int64_t)num_kv_heads * head_size,
+             "%s: token strides must be multiples of 8 elements and cover one row", fn);
+  AICI_CHECK(((uintptr_t)key | (uintptr_t)value | (uintptr_t)key_cache |
+              (uintptr_t)value_cache) % 16 == 0,
+             "%s: tensors must be 16-byte aligned", fn);
+  unsigned int *st = status_ptr();
+  AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
+  dim3 grid((num_tokens + kTok - 1) / kTok, num_kv_heads);
+  gather_cached_kv_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16 *>(key), static_cast<__nv_bfloat16 *>(value),
+      static_cast<const __nv_bfloat16 *>(key_cache),
+      static_cast<const __nv_bfloat16 *>(value_cache), slot_mapping, num_tokens, num_kv_heads,
+      num_blocks * kB, key_stride, value_stride, st);
+  AICI_CUDA(cudaGetLastError());
+  return nullptr;
+}
+
+static char *check_copy(const char *fn, int num_layers, int num_pairs, int64_t numel_per_block,
+                        int dtype) {
+  AICI_CHECK(dtype == AICI_DTYPE_BF16 || dtype == AICI_DTYPE_F16,
+             "%s: cache dtype must be bf16 or f16 (dtype=%d)", fn, dtype);
+  AICI_CHECK(num_layers >= 0 && num_pairs >= 0, "%s: negative count", fn);
+  AICI_CHECK(numel_per_block > 0 && (numel_per_block * 2) % 16 == 0,
+             "%s: a block must be a positive multiple of 16 bytes", fn);
+  AICI_CHECK(num_layers <= 32767, "%s: too many layers (%d)", fn, num_layers);
+  return nullptr;
+}
+
+extern "C" char *aici_copy_blocks(const int64_t *key_cache_ptrs, const int64_t *value_cache_ptrs,
+                                  const int64_t *block_mapping, int num_layers, int num_pairs,
+                                  int64_t numel_per_block, int64_t num_blocks, int dtype,
+                                  aici_stream_t stream) {
+  const char *fn = "aici_copy_blocks";
+  if (char *e = check_copy(fn, num_layers, num_pairs, numel_per_block, dtype)) return e;
+  if (num_layers == 0 || num_pairs == 0) return nullptr;
+  AICI_CHECK(key_cache_ptrs && value_cache_ptrs && block_mapping, "%s: NULL pointer", fn);
+  unsigned int *st = status_ptr();
+  AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
+  dim3 grid(num_pairs, 2 * num_layers);
+  copy_blocks_kernel<<<grid, kCopyThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      key_cache_ptrs, value_cache_ptrs, block_mapping, num_layers, numel_per_block * 2, num_blocks,
+      st);
+  AICI_CUDA(cudaGetLastError());
+  return nullptr;
+}
+
+extern "C" char *aici_copy_blocks_host(const int64_t *key_cache_ptrs_host,
+                                       const int64_t *value_cache_ptrs_host,
+                                       const int64_t *block_mapping_host, int num_layers,
+                                       int num_pairs, int64_t numel_per_block, int64_t num_blocks,
+                                       int dtype, aici_stream_t stream) {
+  const char *fn = "aici_copy_blocks_host";
+  if (char *e = check_copy(fn, num_layers, num_pairs, numel_per_block, dtype)) return e;
+  if (num_layers == 0 || num_pairs == 0) return nullptr;
+  AICI_CHECK(key_cache_ptrs_host && value_cache_ptrs_host && block_mapping_host,
+             "%s: NULL pointer", fn);
+  for (int p = 0; p < num_pairs; ++p) {
+    const int64_t src = block_mapping_host[2 * p], dst = block_mapping_host[2 * p + 1];
+    AICI_CHECK(src >= 0 && dst >= 0 && src <= INT32_MAX && dst <= INT32_MAX &&
+                   (num_blocks <= 0 || (src < num_blocks && dst < num_blocks)),
+               "%s: pair %d (%lld -> %lld) is outside the cache of %lld blocks", fn, p,
+               (long long)src, (long long)dst, (long long)num_blocks);
+  }
+  for (int l = 0; l < num_layers; ++l)
+    AICI_CHECK(key_cache_ptrs_host[l] % 16 == 0 && value_cache_ptrs_host[l] % 16 == 0 &&
+                   key_cache_ptrs_host[l] != 0 && value_cache_ptrs_host[l] != 0,
+               "%s: layer %d cache base must be non-NULL and 16-byte aligned", fn, l);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int l0 = 0; l0 < num_layers; l0 += kArgLayers) {
+    const int nl = num_layers - l0 < kArgLayers ? num_layers - l0 : kArgLayers;
+    for (int p0 = 0; p0 < num_pairs; p0 += kArgPairs) {
+      const int np = num_pairs - p0 < kArgPairs ? num_pairs - p0 : kArgPairs;
+      CopyArgs args;
+      memset(&args, 0, sizeof(args));
+      for (int l = 0; l < nl; ++l) {
+        args.key_ptrs[l] = key_cache_ptrs_host[l0 + l];
+        args.value_ptrs[l] = value_cache_ptrs_host[l0 + l];
+      }
+      for (int p = 0; p < np; ++p) {
+        args.src[p] = static_cast<int32_t>(block_mapping_host[2 * (p0 + p)]);
+        args.dst[p] = static_cast<int32_t>(block_mapping_host[2 * (p0 + p) + 1]);
+      }
+      dim3 grid(np, 2 * nl);
+      copy_blocks_args_kernel<<<grid, kCopyThreads, 0, s>>>(args, nl, numel_per_block * 2);
+      AICI_CUDA(cudaGetLastError());
+    }
+  }
+  return nullptr;
+}

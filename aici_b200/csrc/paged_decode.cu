@@ -1,0 +1,615 @@
+// Decode attention over the paged KV cache for sm_100a (one query token per sequence).
+//
+// Semantics follow rllm/tch-cuda/kernels/vllm/attention/attention_kernels.cu
+// (paged_attention_kernel :85-392, v2 reduce :450-546): fp32 logits scale*q.k over
+// t < context_len, softmax with the reference's +1e-6 in the denominator, fp32 accumulation
+// of p*V, kv head = head / (num_heads / num_kv_heads).
+//
+// The traversal is new.  The unit of work is one (sequence, kv head, chunk of the context);
+// every warp is an independent streaming agent:
+//   * lane 0 issues 1-D bulk copies (cp.async.bulk, completion on an mbarrier) that bring
+//     the 4 KB key tile and the 4 KB value tile of one 16-token cache block into the warp's
+//     private shared-memory ring, kStages deep, running ahead across work items;
+//   * the warp multiplies the whole query-head group of that kv head against the tile with
+//     bf16 mma.sync (q heads are the M rows, padded to 16), keeps an online softmax per row
+//     in registers (warp shuffles for the row max/sum), and accumulates P*V in fp32;
+//   * at the end of a chunk it writes either the final row (single-chunk sequences) or an
+//     fp32 partial (max, sum, normalised output) that a merge kernel combines.
+// So K/V are read from HBM exactly once per (sequence, kv head) regardless of the group
+// size, every byte moves as a 4 KB contiguous burst, and long contexts are split so that
+// all warps of all SMs carry the same amount of work.
+#include "common.cuh"
+
+namespace aici {
+
+constexpr int kD = 128;
+constexpr int kB = 16;
+constexpr int kTileBytes = kD * kB * 2;     // 4096: one (block, kv head) key or value tile
+constexpr int kStageBytes = 2 * kTileBytes; // key tile + value tile
+constexpr int kWarps = 4;                   // warps per CTA, each with a private ring
+constexpr int kStages = 3;                  // ring depth per warp
+constexpr int kMaxChunk = 512;              // tokens; 32 tiles, one block id per lane
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct DecodeParams {
+  const __nv_bfloat16 *q;
+  const __nv_bfloat16 *k_cache;
+  const __nv_bfloat16 *v_cache;
+  __nv_bfloat16 *out;
+  const int32_t *block_tables;
+  const int32_t *context_lens;
+  const int2 *entries;   // compacted (seq, chunk) list, or NULL: every (seq, chunk < max_parts)
+  const int *n_entries;  // device count for `entries`
+  float *part_max;       // [num_seqs, num_heads, max_parts] natural-log-domain max logit
+  float *part_sum;       // [num_seqs, num_heads, max_parts] sum of exp(logit - max)
+  void *part_out;        // [num_seqs, num_heads, max_parts, 128] fp32 or bf16, normalised
+  int num_seqs, num_heads, num_kv_heads, group;
+  int max_blocks_per_seq;
+  int max_context_len;
+  int64_t num_blocks;
+  int chunk_tokens;
+  int max_parts;
+  int always_write_partials;  // v2 calling convention: partials are an output too
+  int64_t q_stride, kv_block_stride, kv_head_stride;
+  float scale_log2e;
+  unsigned int *status;
+};
+
+struct Item {
+  int seq, chunk, kvh, ctx, tok0, ntiles;
+};
+
+__device__ __forceinline__ int clamp_ctx(const DecodeParams &p, int ctx) {
+  int lim = p.max_context_len;
+  const int cap = p.max_blocks_per_seq * kB;
+  if (cap < lim) lim = cap;
+  if (ctx > lim) {
+    set_status(p.status, AICI_STATUS_BAD_BLOCK);
+    ctx = lim;
+  }
+  return ctx < 0 ? 0 : ctx;
+}
+
+// Decodes work item `idx`; ntiles == 0 marks an empty one (virtual grid only).
+__device__ __forceinline__ void fetch_item(const DecodeParams &p, int idx, Item &it) {
+  const int e = idx / p.num_kv_heads;
+  it.kvh = idx - e * p.num_kv_heads;
+  if (p.entries != nullptr) {
+    const int2 sc = p.entries[e];
+    it.seq = sc.x;
+    it.chunk = sc.y;
+  } else {
+    it.seq = e / p.max_parts;
+    it.chunk = e - it.seq * p.max_parts;
+  }
+  it.ctx = clamp_ctx(p, p.context_lens[it.seq]);
+  it.tok0 = it.chunk * p.chunk_tokens;
+  int n = it.ctx - it.tok0;
+  if (n > p.chunk_tokens) n = p.chunk_tokens;
+  it.ntiles = n > 0 ? (n + kB - 1) / kB : 0;
+}
+
+template <typename PartT>
+__device__ __forceinline__ void store_pair(PartT *dst, float a, float b);
+template <>
+__device__ __forceinline__ void store_pair<float>(float *dst, float a, float b) {
+  *reinterpret_cast<float2 *>(dst) = make_float2(a, b);
+}
+template <>
+__device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloat16 *dst, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162 *>(dst) = __floats2bfloat162_rn(a, b);
+}
+
+template <typename PartT>
+__global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  uint8_t *ring = smem + warp * (kStages * kStageBytes);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + kWarps * kStages * kStageBytes) + warp * kStages;
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+
+  const int n_entries = p.entries != nullptr ? *p.n_entries : p.num_seqs * p.max_parts;
+  const int n_items = n_entries * p.num_kv_heads;
+  const int stride = gridDim.x * kWarps;
+  const int gw = blockIdx.x * kWarps + warp;
+
+  // ---- producer cursor ---------------------------------------------------------------
+  int p_idx = gw - stride;
+  Item p_item;
+  p_item.ntiles = 0;
+  p_item.kvh = 0;
+  int p_tile = 0, p_blk = 0;
+  unsigned p_count = 0;
+  bool p_done = false;
+
+  auto produce_one = [&]() {
+    if (p_done) return;
+    if (p_tile == p_item.ntiles) {
+      do {
+        p_idx += stride;
+        if (p_idx >= n_items) {
+          p_done = true;
+          return;
+        }
+        fetch_item(p, p_idx, p_item);
+      } while (p_item.ntiles == 0);
+      int b = 0;
+      if (lane < p_item.ntiles) {
+        b = p.block_tables[(int64_t)p_item.seq * p.max_blocks_per_seq + p_item.tok0 / kB + lane];
+        if (b < 0 || b >= p.num_blocks) {
+          set_status(p.status, AICI_STATUS_BAD_BLOCK);
+          b = 0;
+        }
+      }
+      p_blk = b;
+      p_tile = 0;
+    }
+    const int blk = __shfl_sync(0xffffffffu, p_blk, p_tile);
+    if (lane == 0) {
+      const unsigned stage = p_count % kStages;
+      uint8_t *dst = ring + stage * kStageBytes;
+      const int64_t off = (int64_t)blk * p.kv_block_stride + (int64_t)p_item.kvh * p.kv_head_stride;
+      fence_proxy_async_smem();  // order this warp's earlier reads of the stage before the refill
+      mbar_expect_tx(&full[stage], kStageBytes);
+      bulk_g2s(dst, p.k_cache + off, kTileBytes, &full[stage]);
+      bulk_g2s(dst + kTileBytes, p.v_cache + off, kTileBytes, &full[stage]);
+    }
+    ++p_tile;
+    ++p_count;
+  };
+
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) produce_one();
+
+  // ldmatrix lane offsets: lane -> (matrix mi = lane / 8, row = lane % 8)
+  const int mi = lane >> 3, mr = lane & 7;
+  // key tile [c = d/8][tok][8]: matrices (c even, tok 0-7), (c odd, tok 0-7), (c even, tok 8-15), (c odd, tok 8-15)
+  const uint32_t k_lane_off = (((mi & 1) * kB) + 8 * (mi >> 1) + mr) * 16;
+  // value tile [d][tok]: matrices (d 0-7, tok 0-7), (d 0-7, tok 8-15), (d 8-15, tok 0-7), (d 8-15, tok 8-15)
+  const uint32_t v_lane_off = (8 * (mi >> 1) + mr) * 32 + (mi & 1) * 16;
+
+  unsigned c_count = 0;
+  int c_idx = gw - stride;
+  bool failed = false;
+
+  while (!failed) {
+    Item it;
+    do {
+      c_idx += stride;
+      if (c_idx >= n_items) break;
+      fetch_item(p, c_idx, it);
+    } while (it.ntiles == 0);
+    if (c_idx >= n_items) break;
+
+    // query fragments: rows = heads of this kv head's group (rows >= group are zero)
+    uint32_t qa[8][2];
+    {
+      const __nv_bfloat16 *qrow =
+          p.q + (int64_t)it.seq * p.q_stride + (int64_t)(it.kvh * p.group + g) * kD + 2 * tig;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        if (g < p.group) {
+          qa[ks][0] = *reinterpret_cast<const uint32_t *>(qrow + 16 * ks);
+          qa[ks][1] = *reinterpret_cast<const uint32_t *>(qrow + 16 * ks + 8);
+        } else {
+          qa[ks][0] = 0u;
+          qa[ks][1] = 0u;
+        }
+      }
+    }
+
+    float o[16][4];
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+
+    for (int t = 0; t < it.ntiles; ++t) {
+      produce_one();
+      const unsigned stage = c_count % kStages;
+      if (!__all_sync(0xffffffffu, mbar_wait(&full[stage], (c_count / kStages) & 1u, p.status))) {
+        failed = true;
+        break;
+      }
+      const uint32_t kbase = smem_u32(ring + stage * kStageBytes);
+      const uint32_t vbase = kbase + kTileBytes;
+
+      // ---- S = Q K^T (16 x 16) -------------------------------------------------------
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t b00, b01, b10, b11;
+        ldmatrix_x4(b00, b01, b10, b11, kbase + ks * (2 * kB * 16) + k_lane_off);
+        mma_bf16_16816(s0, qa[ks][0], 0u, qa[ks][1], 0u, b00, b01);
+        mma_bf16_16816(s1, qa[ks][0], 0u, qa[ks][1], 0u, b10, b11);
+      }
+
+      // ---- online softmax for row g (scores in log2 units) ----------------------------
+      const int tok_base = it.tok0 + t * kB;
+      const bool last = tok_base + kB > it.ctx;
+      float x00 = s0[0] * p.scale_log2e, x01 = s0[1] * p.scale_log2e;
+      float x10 = s1[0] * p.scale_log2e, x11 = s1[1] * p.scale_log2e;
+      uint32_t vm_lo = 0xffffffffu, vm_hi = 0xffffffffu;
+      if (last) {
+        const int c0 = tok_base + 2 * tig;
+        if (c0 >= it.ctx) { x00 = -INFINITY; vm_lo &= 0xffff0000u; }
+        if (c0 + 1 >= it.ctx) { x01 = -INFINITY; vm_lo &= 0x0000ffffu; }
+        if (c0 + 8 >= it.ctx) { x10 = -INFINITY; vm_hi &= 0xffff0000u; }
+        if (c0 + 9 >= it.ctx) { x11 = -INFINITY; vm_hi &= 0x0000ffffu; }
+      }
+      float mt = fmaxf(fmaxf(x00, x01), fmaxf(x10, x11));
+      mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
+      mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
+      const float m_new = fmaxf(m_run, mt);
+      if (!__all_sync(0xffffffffu, m_new == m_run)) {
+        const float alpha = fast_exp2(m_run - m_new);  // 0 on the first tile
+        l_run *= alpha;
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) {
+          o[nt][0] *= alpha;
+          o[nt][1] *= alpha;
+        }
+        m_run = m_new;
+      }
+      const float p00 = fast_exp2(x00 - m_run), p01 = fast_exp2(x01 - m_run);
+      const float p10 = fast_exp2(x10 - m_run), p11 = fast_exp2(x11 - m_run);
+      l_run += (p00 + p01) + (p10 + p11);
+      const uint32_t pa0 = pack_bf16(p00, p01), pa2 = pack_bf16(p10, p11);
+
+      // ---- O += P V (16 x 128) ---------------------------------------------------------
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        uint32_t v00, v01, v10, v11;
+        ldmatrix_x4(v00, v01, v10, v11, vbase + np * (16 * 32) + v_lane_off);
+        if (last) {  // cache slots past the context may hold anything, NaN included
+          v00 &= vm_lo; v10 &= vm_lo;
+          v01 &= vm_hi; v11 &= vm_hi;
+        }
+        mma_bf16_16816(o[2 * np], pa0, 0u, pa2, 0u, v00, v01);
+        mma_bf16_16816(o[2 * np + 1], pa0, 0u, pa2, 0u, v10, v11);
+      }
+      __syncwarp();
+      ++c_count;
+    }
+    if (failed) break;
+
+    // ---- chunk epilogue ----------------------------------------------------------------
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (g < p.group) {
+      const int head = it.kvh * p.group + g;
+      const float inv = __fdividef(1.f, l_run + 1e-6f);
+      const int n_chunks = (it.ctx + p.chunk_tokens - 1) / p.chunk_tokens;
+      if (n_chunks == 1) {
+        __nv_bfloat16 *dst = p.out + ((int64_t)it.seq * p.num_heads + head) * kD + 2 * tig;
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt)
+          store_pair<__nv_bfloat16>(dst + 8 * nt, o[nt][0] * inv, o[nt][1] * inv);
+      }
+      if (n_chunks > 1 || p.always_write_partials) {
+        const int64_t pidx = ((int64_t)it.seq * p.num_heads + head) * p.max_parts + it.chunk;
+        if (tig == 0) {
+          p.part_max[pidx] = m_run * kLn2;
+          p.part_sum[pidx] = l_run;
+        }
+        PartT *dst = static_cast<PartT *>(p.part_out) + pidx * kD + 2 * tig;
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) store_pair<PartT>(dst + 8 * nt, o[nt][0] * inv, o[nt][1] * inv);
+      }
+    }
+  }
+
+  if (failed) {
+    // give copies already in flight a bounded chance to land before the ring is released
+    for (unsigned c = c_count; c != p_count; ++c)
+      mbar_wait(&full[c % kStages], (c / kStages) & 1u, p.status);
+  }
+}
+
+// Combines the chunk partials of one (sequence, head): v2 reduce of the reference.
+template <typename PartT>
+__global__ void __launch_bounds__(kD) paged_merge_kernel(const DecodeParams p) {
+  const int head = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+  const int ctx = clamp_ctx(p, p.context_lens[seq]);
+  const int n = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
+  if (n == 1) return;  // the decode kernel wrote the row itself
+  __nv_bfloat16 *dst = p.out + ((int64_t)seq * p.num_heads + head) * kD + d;
+  if (n <= 0) {
+    *dst = __float2bfloat16(0.f);
+    return;
+  }
+  const int64_t base = ((int64_t)seq * p.num_heads + head) * p.max_parts;
+  float m = -INFINITY;
+  for (int j = 0; j < n; ++j) m = fmaxf(m, p.part_max[base + j]);
+  float wsum = 0.f, acc = 0.f;
+  const PartT *po = static_cast<const PartT *>(p.part_out) + base * kD + d;
+  for (int j = 0; j < n; ++j) {
+    const float w = p.part_sum[base + j] * __expf(p.part_max[base + j] - m);
+    wsum += w;
+    acc += w * static_cast<float>(po[(int64_t)j * kD]);
+  }
+  *dst = __float2bfloat16(acc * __fdividef(1.f, wsum + 1e-6f));
+}
+
+// Builds the compact (seq, chunk) list so that every warp of the decode kernel gets the same
+// number of non-empty chunks.  One CTA; order = sequences ascending, chunks ascending.
+__global__ void __launch_bounds__(1024) paged_plan_kernel(const DecodeParams p, int2 *entries,
+                                                          int *n_entries) {
+  __shared__ int s_warp[32];
+  __shared__ int s_base;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) s_base = 0;
+  __syncthreads();
+  for (int s0 = 0; s0 < p.num_seqs; s0 += 1024) {
+    const int seq = s0 + tid;
+    int cnt = 0;
+    if (seq < p.num_seqs) {
+      const int ctx = clamp_ctx(p, p.context_lens[seq]);
+      cnt = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
+    }
+    int incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += v;
+      }
+      s_warp[lane] = w;
+    }
+    __syncthreads();
+    const int base = s_base + (warp > 0 ? s_warp[warp - 1] : 0) + incl - cnt;
+    for (int c = 0; c < cnt; ++c) entries[base + c] = make_int2(seq, c);
+    __syncthreads();
+    if (tid == 0) s_base += s_warp[31];
+    __syncthreads();
+  }
+  if (tid == 0) *n_entries = s_base;
+}
+
+// ---- host side -------------------------------------------------------------------------------
+static int g_chunk_override = 0;
+
+static int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+static int pick_chunk(int max_context_len) {
+  (void)max_context_len;
+  if (g_chunk_override > 0) return g_chunk_override;
+  return 256;
+}
+
+constexpr size_t kAlign = 256;
+static size_t align_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+struct WorkspaceLayout {
+  size_t n_entries_off, entries_off, max_off, sum_off, out_off, total;
+  int max_parts;
+};
+
+static WorkspaceLayout workspace_layout(int num_seqs, int num_heads, int max_context_len,
+                                        int chunk) {
+  WorkspaceLayout w;
+  w.max_parts = max_context_len > 0 ? (max_context_len + chunk - 1) / chunk : 1;
+  const size_t parts = (size_t)num_seqs * w.max_parts;
+  w.n_entries_off = 0;
+  w.entries_off = kAlign;
+  w.max_off = w.entries_off + align_up(parts * sizeof(int2));
+  w.sum_off = w.max_off + align_up(parts * num_heads * sizeof(float));
+  w.out_off = w.sum_off + align_up(parts * num_heads * sizeof(float));
+  w.total = w.out_off + align_up(parts * num_heads * kD * sizeof(float));
+  return w;
+}
+
+static char *check_decode_args(const char *fn, const void *out, const void *query,
+                               const void *key_cache, const void *value_cache, int num_kv_heads,
+                               const int32_t *block_tables, const int32_t *context_lens,
+                               int block_size, int max_context_len, const float *alibi_slopes,
+                               int num_seqs, int num_heads, int head_size,
+                               int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_stride,
+                               int64_t kv_block_stride, int64_t kv_head_stride, int dtype) {
+  AICI_CHECK(dtype == AICI_DTYPE_BF16, "%s: only bf16 is supported (dtype=%d)", fn, dtype);
+  AICI_CHECK(head_size == kD, "%s: Unsupported head size: %d", fn, head_size);
+  AICI_CHECK(block_size == kB, "%s: Unsupported block size: %d", fn, block_size);
+  AICI_CHECK(alibi_slopes == nullptr, "%s: alibi_slopes is not supported", fn);
+  AICI_CHECK(num_seqs >= 0 && num_heads > 0 && num_kv_heads > 0, "%s: bad sizes", fn);
+  AICI_CHECK(num_heads % num_kv_heads == 0, "%s: num_heads %d not divisible by num_kv_heads %d",
+             fn, num_heads, num_kv_heads);
+  const int group = num_heads / num_kv_heads;
+  AICI_CHECK(group == 1 || group == 2 || group == 4 || group == 8,
+             "%s: num_heads / num_kv_heads must be 1, 2, 4 or 8 (got %d)", fn, group);
+  if (num_seqs == 0) return nullptr;
+  AICI_CHECK(out && query && key_cache && value_cache && block_tables && context_lens,
+             "%s: NULL pointer", fn);
+  AICI_CHECK(max_context_len >= 0 && max_num_blocks_per_seq >= 0, "%s: negative size", fn);
+  AICI_CHECK(num_blocks > 0, "%s: num_blocks must be positive", fn);
+  AICI_CHECK(q_stride % 8 == 0 && q_stride >= (int64_t)num_heads * kD,
+             "%s: q_stride must be a multiple of 8 and cover one row", fn);
+  AICI_CHECK(kv_head_stride == kD * kB && kv_block_stride % 8 == 0 &&
+                 kv_block_stride >= (int64_t)num_kv_heads * kD * kB,
+             "%s: cache must be [blocks, kv_heads, 128/8, 16, 8] with contiguous head tiles", fn);
+  AICI_CHECK(((uintptr_t)out | (uintptr_t)query | (uintptr_t)key_cache |
+              (uintptr_t)value_cache) % 16 == 0,
+             "%s: tensors must be 16-byte aligned", fn);
+  AICI_CHECK((int64_t)num_seqs * ((max_context_len + 127) / 128 + 1) * num_kv_heads < (1ll << 30),
+             "%s: problem too large for 32-bit work indices", fn);
+  return nullptr;
+}
+
+template <typename PartT>
+static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaStream_t stream) {
+  static bool attr_set[64] = {false};
+  const int smem = kWarps * kStages * kStageBytes + kWarps * kStages * (int)sizeof(uint64_t);
+  int dev = 0;
+  AICI_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    AICI_CUDA(cudaFuncSetAttribute(paged_decode_kernel<PartT>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set[dev] = true;
+  }
+  if (entries != nullptr) {
+    paged_plan_kernel<<<1, 1024, 0, stream>>>(p, entries, n_entries);
+    AICI_CUDA(cudaGetLastError());
+  }
+  p.entries = entries;
+  p.n_entries = n_entries;
+  const int64_t ub_items = (int64_t)p.num_seqs * p.max_parts * p.num_kv_heads;
+  int grid = 2 * sm_count();
+  const int64_t need = (ub_items + kWarps - 1) / kWarps;
+  if (need < grid) grid = (int)need;
+  if (grid < 1) grid = 1;
+  paged_decode_kernel<PartT><<<grid, kWarps * 32, smem, stream>>>(p);
+  AICI_CUDA(cudaGetLastError());
+  paged_merge_kernel<PartT><<<dim3(p.num_heads, p.num_seqs), kD, 0, stream>>>(p);
+  AICI_CUDA(cudaGetLastError());
+  return nullptr;
+}
+
+}  // namespace aici
+
+using namespace aici;
+
+// Tuning hook for benchmarks: tokens per split chunk (multiple of 16, <= 512); 0 = default.
+extern "C" char *aici_tune_decode_chunk(int chunk_tokens) {
+  AICI_CHECK(chunk_tokens == 0 || (chunk_tokens % kB == 0 && chunk_tokens > 0 &&
+                                   chunk_tokens <= kMaxChunk),
+             "aici_tune_decode_chunk: chunk must be 0 or a multiple of 16 up to 512");
+  g_chunk_override = chunk_tokens;
+  return nullptr;
+}
+
+extern "C" size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads,
+                                                       int max_context_len) {
+  if (num_seqs <= 0 || num_heads <= 0) return kAlign;
+  return workspace_layout(num_seqs, num_heads, max_context_len, pick_chunk(max_context_len)).total;
+}
+
+extern "C" char *aici_paged_attention_v1(void *out, const void *query, const void *key_cache,
+                                         const void *value_cache, int num_kv_heads, float scale,
+                                         const int32_t *block_tables, const int32_t *context_lens,
+                                         int block_size, int max_context_len,
+                                         const float *alibi_slopes, int num_seqs, int num_heads,
+                                         int head_size, int max_num_blocks_per_seq,
+                                         int64_t num_blocks, int64_t q_stride,
+                                         int64_t kv_block_stride, int64_t kv_head_stride,
+                                         void *workspace, size_t workspace_bytes, int dtype,
+                                         aici_stream_t stream) {
+  const char *fn = "aici_paged_attention_v1";
+  if (char *e = check_decode_args(fn, out, query, key_cache, value_cache, num_kv_heads,
+                                  block_tables, context_lens, block_size, max_context_len,
+                                  alibi_slopes, num_seqs, num_heads, head_size,
+                                  max_num_blocks_per_seq, num_blocks, q_stride, kv_block_stride,
+                                  kv_head_stride, dtype))
+    return e;
+  if (num_seqs == 0) return nullptr;
+  const int chunk = pick_chunk(max_context_len);
+  const WorkspaceLayout w = workspace_layout(num_seqs, num_heads, max_context_len, chunk);
+  AICI_CHECK(workspace != nullptr && workspace_bytes >= w.total,
+             "%s: workspace too small (%zu bytes given, %zu needed)", fn, workspace_bytes, w.total);
+  AICI_CHECK((uintptr_t)workspace % kAlign == 0, "%s: workspace must be 256-byte aligned", fn);
+  unsigned int *st = status_ptr();
+  AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
+  char *ws = static_cast<char *>(workspace);
+  DecodeParams p;
+  p.q = static_cast<const __nv_bfloat16 *>(query);
+  p.k_cache = static_cast<const __nv_bfloat16 *>(key_cache);
+  p.v_cache = static_cast<const __nv_bfloat16 *>(value_cache);
+  p.out = static_cast<__nv_bfloat16 *>(out);
+  p.block_tables = block_tables;
+  p.context_lens = context_lens;
+  p.part_max = reinterpret_cast<float *>(ws + w.max_off);
+  p.part_sum = reinterpret_cast<float *>(ws + w.sum_off);
+  p.part_out = ws + w.out_off;
+  p.num_seqs = num_seqs;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.group = num_heads / num_kv_heads;
+  p.max_blocks_per_seq = max_num_blocks_per_seq;
+  p.max_context_len = max_context_len;
+  p.num_blocks = num_blocks;
+  p.chunk_tokens = chunk;
+  p.max_parts = w.max_parts;
+  p.always_write_partials = 0;
+  p.q_stride = q_stride;
+  p.kv_block_stride = kv_block_stride;
+  p.kv_head_stride = kv_head_stride;
+  p.scale_log2e = scale * kLog2e;
+  p.status = st;
+  return launch_decode<float>(p, reinterpret_cast<int2 *>(ws + w.entries_off),
+                              reinterpret_cast<int *>(ws + w.n_entries_off),
+                              static_cast<cudaStream_t>(stream));
+}
+
+extern "C" char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_logits,
+                                         void *tmp_out, const void *query, const void *key_cache,
+                                         const void *value_cache, int num_kv_heads, float scale,
+                                         const int32_t *block_tables, const int32_t *context_lens,
+                                         int block_size, int max_context_len,
+                                         const float *alibi_slopes, int num_seqs, int num_heads,
+                                         int head_size, int max_num_blocks_per_seq,
+                                         int64_t num_blocks, int64_t q_stride,
+                                         int64_t kv_block_stride, int64_t kv_head_stride,
+                                         int dtype, aici_stream_t stream) {
+  const char *fn = "aici_paged_attention_v2";
+  if (char *e = check_decode_args(fn, out, query, key_cache, value_cache, num_kv_heads,
+                                  block_tables, context_lens, block_size, max_context_len,
+                                  alibi_slopes, num_seqs, num_heads, head_size,
+                                  max_num_blocks_per_seq, num_blocks, q_stride, kv_block_stride,
+                                  kv_head_stride, dtype))
+    return e;
+  if (num_seqs == 0) return nullptr;
+  AICI_CHECK(exp_sums && max_logits && tmp_out, "%s: NULL pointer", fn);
+  AICI_CHECK((uintptr_t)tmp_out % 4 == 0, "%s: tmp_out must be 4-byte aligned", fn);
+  unsigned int *st = status_ptr();
+  AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
+  DecodeParams p;
+  p.q = static_cast<const __nv_bfloat16 *>(query);
+  p.k_cache = static_cast<const __nv_bfloat16 *>(key_cache);
+  p.v_cache = static_cast<const __nv_bfloat16 *>(value_cache);
+  p.out = static_cast<__nv_bfloat16 *>(out);
+  p.block_tables = block_tables;
+  p.context_lens = context_lens;
+  p.part_max = max_logits;
+  p.part_sum = exp_sums;
+  p.part_out = tmp_out;
+  p.num_seqs = num_seqs;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.group = num_heads / num_kv_heads;
+  p.max_blocks_per_seq = max_num_blocks_per_seq;
+  p.max_context_len = max_context_len;
+  p.num_blocks = num_blocks;
+  p.chunk_tokens = 512;  // PARTITION_SIZE of the reference
+  p.max_parts = max_context_len > 0 ? (max_context_len + 511) / 512 : 1;
+  p.always_write_partials = 1;
+  p.q_stride = q_stride;
+  p.kv_block_stride = kv_block_stride;
+  p.kv_head_stride = kv_head_stride;
+  p.scale_log2e = scale * kLog2e;
+  p.status = st;
+  return launch_decode<__nv_bfloat16>(p, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}

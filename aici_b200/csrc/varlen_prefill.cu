@@ -1,0 +1,427 @@
+// Variable-length causal prefill attention for sm_100a: tcgen05 MMA with TMEM accumulators,
+// operands staged by TMA, online softmax in registers.
+//
+// Semantics follow mha_varlen_fwd of rllm/tch-cuda/kernels/flash_attn (flash_api.cpp:447-618,
+// flash_fwd_kernel.h:590-1136): O = softmax(scale * Q K^T + causal mask) V per packed sequence
+// and head, fp32 scores and accumulation, probabilities rounded to bf16 before P V, kv head =
+// head / (num_heads / num_heads_k), causal mask aligned to the bottom-right corner
+// (softmax.h:159-168), rows that see no column give 0 (flash_fwd_kernel.h:1056).
+//
+// One CTA owns one 128-row query tile of one (sequence, head) and walks its key/value tiles of
+// 128 tokens.  Two CTAs share an SM (96 KB of shared memory and 256 TMEM columns each), so one
+// CTA's softmax overlaps the other's tensor-core work.
+//   warp 4   : TMA producer (Q once, then K_j and V_j into single buffers, 128B-swizzled)
+//   warp 5   : TMEM owner and MMA issuer: S = Q K_j^T (SS form), then O += P_j V_j with P read
+//              from TMEM (TS form) and V as an MN-major shared-memory operand
+//   warps 0-3: one query row per thread (= one TMEM lane): read S with tcgen05.ld, mask, running
+//              max with lazy rescale of O, exp2, row sum, bf16 P written back over S with
+//              tcgen05.st; at the end O / sum -> bf16 -> swizzled staging -> coalesced stores
+// Every barrier wait is bounded; a timeout sets AICI_STATUS_WAIT_TIMEOUT and unwinds.
+#include "tcgen05.cuh"
+
+namespace aici {
+
+constexpr int kBM = 128;               // query rows per CTA
+constexpr int kBN = 128;               // keys per tile
+constexpr int kHD = 128;               // head size
+constexpr int kPanelBytes = 128 * 128; // [128 rows][64 bf16] = one 128B-swizzled panel
+constexpr int kTileBytes = 2 * kPanelBytes;
+constexpr int kPrefillThreads = 192;
+constexpr uint32_t kTmemCols = 256;    // S/P: columns [0,128), O: columns [128,256)
+constexpr float kRescaleThreshold = 8.f;  // log2 units; P stays below 2^8 between rescales
+
+struct PrefillParams {
+  __nv_bfloat16 *out;
+  const int32_t *cu_q;
+  const int32_t *cu_k;
+  int64_t o_tok_stride, o_head_stride;
+  int group;
+  int causal;
+  float scale_log2e;
+  unsigned int *status;
+};
+
+struct PrefillSmem {
+  uint64_t q_full, k_full, v_full, k_empty, v_empty, s_full, p_ready, o_full, staged;
+  uint32_t tmem_base;
+  uint32_t aborted;
+};
+
+constexpr int kPrefillSmemBytes = 3 * kTileBytes + 1024 /*align*/ + 256 /*PrefillSmem*/;
+
+__global__ void __launch_bounds__(kPrefillThreads, 2)
+varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                      const __grid_constant__ CUtensorMap tmap_k,
+                      const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.z, h = blockIdx.y, hk = h / p.group;
+  const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], lk = p.cu_k[b + 1] - k0;
+  const int n_mblocks = (lq + kBM - 1) / kBM;
+  if ((int)blockIdx.x >= n_mblocks) return;
+  const int m0 = (n_mblocks - 1 - (int)blockIdx.x) * kBM;  // longest causal tiles first
+  const int rows = min(kBM, lq - m0);
+
+  int lim_tile = lk;
+  if (p.causal) lim_tile = min(lk, m0 + rows + lk - lq);
+  const int n_tiles = lim_tile > 0 ? (lim_tile + kBN - 1) / kBN : 0;
+
+  if (n_tiles == 0 || (*reinterpret_cast<volatile unsigned int *>(p.status) & AICI_STATUS_WAIT_TIMEOUT)) {
+    // nothing visible (or the device already reported a stuck pipeline): rows are zero
+    for (int i = tid; i < rows * (kHD / 8); i += kPrefillThreads) {
+      const int r = i / (kHD / 8), c = i % (kHD / 8);
+      *reinterpret_cast<uint4 *>(p.out + (int64_t)(q0 + m0 + r) * p.o_tok_stride +
+                                 (int64_t)h * p.o_head_stride + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t *sQ = smem, *sK = smem + kTileBytes, *sV = smem + 2 * kTileBytes;
+  PrefillSmem *sh = reinterpret_cast<PrefillSmem *>(smem + 3 * kTileBytes);
+
+  if (tid == 0) {
+    mbar_init(&sh->q_full, 1);
+    mbar_init(&sh->k_full, 1);
+    mbar_init(&sh->v_full, 1);
+    mbar_init(&sh->k_empty, 1);
+    mbar_init(&sh->v_empty, 1);
+    mbar_init(&sh->s_full, 1);
+    mbar_init(&sh->p_ready, 4);
+    mbar_init(&sh->o_full, 1);
+    mbar_init(&sh->staged, 4);
+    sh->aborted = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&sh->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == 4) {
+    // ---------------------------------------------------------------- TMA producer -----------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_q);
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_v);
+      mbar_expect_tx(&sh->q_full, kTileBytes);
+      tma_load_3d(sQ, &tmap_q, 0, h, q0 + m0, &sh->q_full);
+      tma_load_3d(sQ + kPanelBytes, &tmap_q, 64, h, q0 + m0, &sh->q_full);
+      for (int j = 0; j < n_tiles; ++j) {
+        const uint32_t ph = (uint32_t)j & 1u;
+        if (!mbar_wait_abortable(&sh->k_empty, ph ^ 1u, p.status)) break;
+        mbar_expect_tx(&sh->k_full, kTileBytes);
+        tma_load_3d(sK, &tmap_k, 0, hk, k0 + j * kBN, &sh->k_full);
+        tma_load_3d(sK + kPanelBytes, &tmap_k, 64, hk, k0 + j * kBN, &sh->k_full);
+        if (!mbar_wait_abortable(&sh->v_empty, ph ^ 1u, p.status)) break;
+        mbar_expect_tx(&sh->v_full, kTileBytes);
+        tma_load_3d(sV, &tmap_v, 0, hk, k0 + j * kBN, &sh->v_full);
+        tma_load_3d(sV + kPanelBytes, &tmap_v, 64, hk, k0 + j * kBN, &sh->v_full);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------------------------------------------------------- MMA issuer -------------
+    constexpr uint32_t idesc_s = idesc_bf16(kBM, kBN, false);
+    constexpr uint32_t idesc_pv = idesc_bf16(kBM, kHD, true);
+    // Q, K: K-major, rows of 128 B, 8-row groups 1024 B apart; two 64-column panels.
+    const uint64_t qdesc = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+    const uint64_t kdesc = smem_desc_sw128(smem_u32(sK), 16, 1024);
+    // V as B operand of P V: N (= d) contiguous, 64 d per swizzle atom, second atom one panel
+    // further (leading offset), 8-token groups 1024 B apart (stride offset).
+    const uint64_t vdesc = smem_desc_sw128(smem_u32(sV), kPanelBytes, 1024);
+    bool ok = __all_sync(0xffffffffu, mbar_wait_abortable(&sh->q_full, 0, p.status));
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      const uint32_t ph = (uint32_t)j & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait_abortable(&sh->k_full, ph, p.status));
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int ks = 0; ks < kHD / 16; ++ks) {
+          const uint64_t adv = (uint64_t)(((ks >> 2) * kPanelBytes + (ks & 3) * 32) >> 4);
+          umma_ss(tmem_base, qdesc + adv, kdesc + adv, idesc_s, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(&sh->k_empty);
+        tc_commit(&sh->s_full);
+      }
+      __syncwarp();
+      ok = mbar_wait_abortable(&sh->p_ready, ph, p.status) &&
+           mbar_wait_abortable(&sh->v_full, ph, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          umma_ts(tmem_base + 128, tmem_base + 8 * ks, vdesc + (uint64_t)((ks * 2048) >> 4),
+                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        tc_commit(&sh->v_empty);
+        if (j == n_tiles - 1) tc_commit(&sh->o_full);
+      }
+      __syncwarp();
+    }
+    if (!ok && lane == 0) sh->aborted = 1;
+  } else {
+    // ---------------------------------------------------------------- softmax / epilogue -----
+    const int row = warp * 32 + lane;
+    const int qr = m0 + row;
+    int lim_row = lk;
+    if (p.causal) lim_row = min(lk, qr + 1 + lk - lq);
+    const uint32_t t_s = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t t_o = t_s + 128;
+    const float sc = p.scale_log2e;
+    float m_used = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = mbar_wait_abortable(&sh->s_full, (uint32_t)j & 1u, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int n0 = j * kBN;
+      uint32_t r[32];
+
+      // pass 1: row max of the raw scores over visible columns
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        tmem_ld32(t_s + 32 * c4, r);
+        tmem_wait_ld();
+        const int cb = n0 + 32 * c4;
+        if (cb + 32 <= lim_row) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (cb + i < lim_row) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      mx *= sc;  // scale > 0, so the order is preserved
+
+      // lazy rescale of the running output
+      if (j == 0) {
+        m_used = mx;
+      } else {
+        const bool need = mx > m_used + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          float alpha = 1.f;
+          if (need) {
+            alpha = fast_exp2(m_used - mx);  // 0 when nothing was visible so far
+            m_used = mx;
+            l_sum *= alpha;
+          }
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            tmem_ld32(t_o + 32 * c4, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(t_o + 32 * c4, r);
+          }
+          tmem_wait_st();
+        }
+      }
+      const float base = (m_used == -INFINITY) ? 0.f : m_used;
+
+      // pass 2: p = exp2(s * scale - base), row sum, bf16 P over the S columns
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        tmem_ld32(t_s + 32 * c4, r);
+        tmem_wait_ld();
+        const int cb = n0 + 32 * c4;
+        uint32_t pk[16];
+        if (cb + 32 <= lim_row) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), sc, -base));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), sc, -base));
+            l_sum += p0 + p1;
+            pk[i >> 1] = pack_bf16(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = (cb + i < lim_row) ? fast_exp2(fmaf(__uint_as_float(r[i]), sc, -base)) : 0.f;
+            const float p1 = (cb + i + 1 < lim_row) ? fast_exp2(fmaf(__uint_as_float(r[i + 1]), sc, -base)) : 0.f;
+            l_sum += p0 + p1;
+            pk[i >> 1] = pack_bf16(p0, p1);
+          }
+        }
+        tmem_st16(t_s + 16 * c4, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->p_ready);
+    }
+
+    if (ok) {
+      ok = mbar_wait_abortable(&sh->o_full, 0, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = l_sum > 0.f ? __fdividef(1.f, l_sum) : 0.f;
+      // staging tile [128 rows][128 bf16] over the Q buffer, 16-byte chunks XOR-swizzled by row
+      uint8_t *stage = sQ;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t r[32];
+        tmem_ld32(t_o + 32 * c4, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(r[8 * q + 0]) * inv, __uint_as_float(r[8 * q + 1]) * inv);
+          v.y = pack_bf16(__uint_as_float(r[8 * q + 2]) * inv, __uint_as_float(r[8 * q + 3]) * inv);
+          v.z = pack_bf16(__uint_as_float(r[8 * q + 4]) * inv, __uint_as_float(r[8 * q + 5]) * inv);
+          v.w = pack_bf16(__uint_as_float(r[8 * q + 6]) * inv, __uint_as_float(r[8 * q + 7]) * inv);
+          const int chunk = 4 * c4 + q;
+          *reinterpret_cast<uint4 *>(stage + row * 256 + ((chunk ^ (row & 7)) << 4)) = v;
+        }
+      }
+      // the four warps meet on an mbarrier (bounded wait) rather than a hardware barrier, so a
+      // warp that unwound early cannot leave the others waiting forever
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->staged);
+      ok = __all_sync(0xffffffffu, mbar_wait(&sh->staged, 0, p.status));
+    }
+    if (ok) {
+      const uint8_t *stage = sQ;
+      __nv_bfloat16 *obase = p.out + (int64_t)(q0 + m0) * p.o_tok_stride + (int64_t)h * p.o_head_stride;
+#pragma unroll 4
+      for (int it = 0; it < 16; ++it) {
+        const int rr = it * 8 + (tid >> 4), chunk = tid & 15;
+        if (rr < rows) {
+          const uint4 v = *reinterpret_cast<const uint4 *>(stage + rr * 256 + ((chunk ^ (rr & 7)) << 4));
+          *reinterpret_cast<uint4 *>(obase + (int64_t)rr * p.o_tok_stride + chunk * 8) = v;
+        }
+      }
+    }
+  }
+
+  // ---- teardown ------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    if (sh->aborted) {
+      // bounded wait for whatever the tensor pipe still owes before the columns are released
+      if (lane == 0) tc_commit(&sh->o_full);
+      __syncwarp();
+      mbar_wait(&sh->o_full, 0, p.status);
+    }
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// [tokens, heads, 128] bf16 with element strides -> 3-D map, box = 64 (d) x 1 (head) x 128 (tokens).
+static char *make_tmap(const char *fn, CUtensorMap *map, const void *base, int64_t tokens, int heads,
+                       int64_t tok_stride, int64_t head_stride) {
+  EncodeTiledFn enc = encode_fn();
+  AICI_CHECK(enc != nullptr, "%s: cuTensorMapEncodeTiled is not available from the driver", fn);
+  cuuint64_t dims[3] = {(cuuint64_t)kHD, (cuuint64_t)heads, (cuuint64_t)tokens};
+  cuuint64_t strides[2] = {(cuuint64_t)head_stride * 2, (cuuint64_t)tok_stride * 2};
+  cuuint32_t box[3] = {64, 1, (cuuint32_t)kBM};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  AICI_CHECK(r == CUDA_SUCCESS, "%s: cuTensorMapEncodeTiled failed with code %d", fn, (int)r);
+  return nullptr;
+}
+
+}  // namespace aici
+
+using namespace aici;
+
+extern "C" char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, const void *v,
+                                     const int32_t *cu_seqlens_q, const int32_t *cu_seqlens_k,
+                                     int batch, int total_q, int total_k, int num_heads,
+                                     int num_heads_k, int head_size, int max_seqlen_q,
+                                     int max_seqlen_k, int64_t q_tok_stride, int64_t q_head_stride,
+                                     int64_t k_tok_stride, int64_t k_head_stride,
+                                     int64_t v_tok_stride, int64_t v_head_stride,
+                                     int64_t o_tok_stride, int64_t o_head_stride,
+                                     float softmax_scale, int is_causal, int dtype,
+                                     aici_stream_t stream) {
+  const char *fn = "aici_mha_varlen_fwd";
+  AICI_CHECK(dtype == AICI_DTYPE_BF16, "%s: FlashAttention only support bf16 data type (dtype=%d)", fn, dtype);
+  AICI_CHECK(batch > 0, "%s: batch size must be positive", fn);
+  AICI_CHECK(head_size == kHD, "%s: head_size must be 128 (got %d)", fn, head_size);
+  AICI_CHECK(num_heads > 0 && num_heads_k > 0 && num_heads % num_heads_k == 0,
+             "%s: Number of heads in key/value must divide number of heads in query", fn);
+  AICI_CHECK(total_q >= 0 && total_k >= 0 && max_seqlen_q >= 0 && max_seqlen_k >= 0, "%s: negative size", fn);
+  AICI_CHECK(softmax_scale > 0.f, "%s: softmax_scale must be positive", fn);
+  AICI_CHECK(batch <= 65535 && num_heads <= 65535, "%s: batch and num_heads must fit a grid dimension", fn);
+  if (total_q == 0 || max_seqlen_q == 0) return nullptr;
+  AICI_CHECK(out && q && cu_seqlens_q && cu_seqlens_k, "%s: NULL pointer", fn);
+  AICI_CHECK(total_k == 0 || (k && v), "%s: NULL pointer", fn);
+  AICI_CHECK(((uintptr_t)out | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % 16 == 0,
+             "%s: tensors must be 16-byte aligned", fn);
+  const int64_t strides[8] = {q_tok_stride, q_head_stride, k_tok_stride, k_head_stride,
+                              v_tok_stride, v_head_stride, o_tok_stride, o_head_stride};
+  for (int i = 0; i < 8; ++i)
+    AICI_CHECK(strides[i] >= kHD && strides[i] % 8 == 0,
+               "%s: token and head strides must be multiples of 8 elements and at least head_size", fn);
+  unsigned int *st = status_ptr();
+  AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
+
+  CUtensorMap tq, tk, tv;
+  if (char *e = make_tmap(fn, &tq, q, total_q, num_heads, q_tok_stride, q_head_stride)) return e;
+  // an empty key tensor still needs a valid map; no tile of it is ever requested
+  const void *kk = total_k > 0 ? k : q;
+  const void *vv = total_k > 0 ? v : q;
+  const int64_t tk_rows = total_k > 0 ? total_k : 1;
+  if (char *e = make_tmap(fn, &tk, kk, tk_rows, num_heads_k, k_tok_stride, k_head_stride)) return e;
+  if (char *e = make_tmap(fn, &tv, vv, tk_rows, num_heads_k, v_tok_stride, v_head_stride)) return e;
+
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  AICI_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    AICI_CUDA(cudaFuncSetAttribute(varlen_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kPrefillSmemBytes));
+    attr_set[dev] = true;
+  }
+  PrefillParams p;
+  p.out = static_cast<__nv_bfloat16 *>(out);
+  p.cu_q = cu_seqlens_q;
+  p.cu_k = cu_seqlens_k;
+  p.o_tok_stride = o_tok_stride;
+  p.o_head_stride = o_head_stride;
+  p.group = num_heads / num_heads_k;
+  p.causal = is_causal ? 1 : 0;
+  p.scale_log2e = softmax_scale * 1.4426950408889634f;
+  p.status = st;
+  dim3 grid((max_seqlen_q + kBM - 1) / kBM, num_heads, batch);
+  varlen_prefill_kernel<<<grid, kPrefillThreads, kPrefillSmemBytes, static_cast<cudaStream_t>(stream)>>>(
+      tq, tk, tv, p);
+  AICI_CUDA(cudaGetLastError());
+  return nullptr;
+}

@@ -1,0 +1,147 @@
+/*
+ * aici_b200 -- C ABI of the B200 (sm_100a) attention path for rLLM.
+ *
+ * These entry points are what rllm/tch-cuda/src/lib.rs would bind in place of the
+ * `*_C(C_tensor*...)` externs (lib.rs:29-47, 106-190).  They take raw device pointers,
+ * explicit sizes and element strides and a CUDA stream; no libtorch type crosses the
+ * boundary.  Every function that can fail returns the reference's error convention
+ * (lib.rs:12-27, kernels/vllm_bindings.cpp:7-13): NULL on success, otherwise a
+ * malloc()-allocated, NUL-terminated message that the caller releases with free().
+ *
+ * Supported shapes: bf16 (AICI_DTYPE_BF16), head_size 128, block_size 16,
+ * num_heads / num_kv_heads in {1, 2, 4, 8}.  Anything else returns an error string; there
+ * is no fallback path.
+ *
+ * KV-cache layout (rllm-cuda/src/llm/paged/cache_engine.rs:81-108), x = 16 / sizeof(T) = 8:
+ *   key_cache   [num_blocks, num_kv_heads, head_size / x, block_size, x]
+ *   value_cache [num_blocks, num_kv_heads, head_size, block_size]
+ */
+#ifndef AICI_B200_H_
+#define AICI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *aici_stream_t; /* cudaStream_t */
+
+enum { AICI_DTYPE_BF16 = 0, AICI_DTYPE_F16 = 1, AICI_DTYPE_F32 = 2 };
+
+/* Sticky device-side status bits, read with aici_last_status(). */
+enum {
+  AICI_STATUS_OK = 0,
+  AICI_STATUS_BAD_BLOCK = 1,   /* a block-table entry was outside [0, num_blocks)        */
+  AICI_STATUS_BAD_SLOT = 2,    /* a slot index was outside the cache                      */
+  AICI_STATUS_WAIT_TIMEOUT = 4 /* a bounded wait on a shared-memory barrier gave up       */
+};
+
+/* Library version string (static storage). */
+const char *aici_version(void);
+
+/* Reads and clears the sticky status word of the current device (synchronises the
+ * device).  Kernels never trap: an out-of-range block or slot is skipped and recorded. */
+char *aici_last_status(int *status_out);
+
+/* ---- KV-cache operations (bit-exact) ------------------------------------------------ */
+
+/* Replaces reshape_and_cache_C (lib.rs:168-174; kernels/vllm/cache_kernels.cu:168-253).
+ * key/value [num_tokens, num_kv_heads, head_size] with token strides in elements.
+ * slot_mapping holds num_tokens entries, int64 when slot_is_int64 != 0 (what the Rust
+ * wrapper passes after its cast, lib.rs:199-200) or int32 (what rLLM builds,
+ * paged/batch_info.rs:203,271).  Negative slots are skipped. */
+char *aici_reshape_and_cache(const void *key, const void *value, void *key_cache,
+                             void *value_cache, const void *slot_mapping, int slot_is_int64,
+                             int num_tokens, int num_kv_heads, int head_size, int block_size,
+                             int64_t num_blocks, int64_t key_stride, int64_t value_stride,
+                             int dtype, aici_stream_t stream);
+
+/* Replaces gather_cached_kv_C (lib.rs:176-182; cache_kernels.cu:301-413): the inverse of
+ * the above with int32 slots. */
+char *aici_gather_cached_kv(void *key, void *value, const void *key_cache,
+                            const void *value_cache, const int32_t *slot_mapping,
+                            int num_tokens, int num_kv_heads, int head_size, int block_size,
+                            int64_t num_blocks, int64_t key_stride, int64_t value_stride,
+                            int dtype, aici_stream_t stream);
+
+/* Replaces copy_blocks_2_C (lib.rs:184-189; cache_kernels.cu:141-163, kernel :55-81).
+ * key_cache_ptrs / value_cache_ptrs: device arrays of num_layers base addresses;
+ * block_mapping: device array of 2*num_pairs int64 (src, dst, src, dst, ...);
+ * numel_per_block = num_kv_heads * head_size * block_size. */
+char *aici_copy_blocks(const int64_t *key_cache_ptrs, const int64_t *value_cache_ptrs,
+                       const int64_t *block_mapping, int num_layers, int num_pairs,
+                       int64_t numel_per_block, int64_t num_blocks, int dtype,
+                       aici_stream_t stream);
+
+/* Same operation with all three arrays in HOST memory: the layer addresses and pairs
+ * travel as kernel arguments, so the three blocking host-to-device uploads the Rust
+ * wrapper makes per call (lib.rs:316-318) disappear.  Replaces tch_cuda::copy_blocks
+ * (lib.rs:276-331) as a whole. */
+char *aici_copy_blocks_host(const int64_t *key_cache_ptrs_host,
+                            const int64_t *value_cache_ptrs_host,
+                            const int64_t *block_mapping_host, int num_layers, int num_pairs,
+                            int64_t numel_per_block, int64_t num_blocks, int dtype,
+                            aici_stream_t stream);
+
+/* ---- decode attention over the paged cache ----------------------------------------- */
+
+/* Bytes of caller-owned scratch aici_paged_attention_v1 needs for these sizes. */
+size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads, int max_context_len);
+
+/* Replaces paged_attention_v1_C (lib.rs:108-120; vllm_bindings.cpp:17-29;
+ * kernels/vllm/attention/attention_kernels.cu:571-700).  out/query
+ * [num_seqs, num_heads, head_size] (q_stride = query row stride in elements; out is
+ * contiguous); block_tables int32 [num_seqs, max_num_blocks_per_seq]; context_lens int32
+ * [num_seqs]; kv_block_stride / kv_head_stride in elements.  alibi_slopes must be NULL
+ * (rLLM never passes one, rllm-cuda/src/llm/mod.rs:310).  The context is always split into
+ * fixed-size chunks that are merged by a second kernel; `workspace` holds the chunk list
+ * and the fp32 partial results and must be at least
+ * aici_paged_attention_workspace_bytes() large and 256-byte aligned. */
+char *aici_paged_attention_v1(void *out, const void *query, const void *key_cache,
+                              const void *value_cache, int num_kv_heads, float scale,
+                              const int32_t *block_tables, const int32_t *context_lens,
+                              int block_size, int max_context_len, const float *alibi_slopes,
+                              int num_seqs, int num_heads, int head_size,
+                              int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_stride,
+                              int64_t kv_block_stride, int64_t kv_head_stride, void *workspace,
+                              size_t workspace_bytes, int dtype, aici_stream_t stream);
+
+/* Replaces paged_attention_v2_C (lib.rs:122-137; vllm_bindings.cpp:31-45;
+ * attention_kernels.cu:729-874).  Partition size 512 as in the reference (:733);
+ * exp_sums / max_logits fp32 [num_seqs, num_heads, P], tmp_out T
+ * [num_seqs, num_heads, P, head_size], P = ceil(max_context_len / 512), filled with the
+ * reference's meaning (partition max logit, partition exp sum, partition-normalised
+ * output) for every partition that holds at least one token. */
+char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_logits, void *tmp_out,
+                              const void *query, const void *key_cache,
+                              const void *value_cache, int num_kv_heads, float scale,
+                              const int32_t *block_tables, const int32_t *context_lens,
+                              int block_size, int max_context_len, const float *alibi_slopes,
+                              int num_seqs, int num_heads, int head_size,
+                              int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_stride,
+                              int64_t kv_block_stride, int64_t kv_head_stride, int dtype,
+                              aici_stream_t stream);
+
+/* ---- variable-length causal prefill attention --------------------------------------- */
+
+/* Replaces mha_varlen_fwd_C (lib.rs:29-47; kernels/flash_attn/flash_api.cpp:622-655,
+ * 447-618).  q/out [total_q, num_heads, head_size], k/v [total_k, num_heads_k, head_size];
+ * token and head strides in elements, last dimension contiguous; cu_seqlens_{q,k} int32
+ * [batch + 1] on the device.  The causal mask is aligned to the bottom-right corner of each
+ * sequence's (len_q x len_k) score matrix.  The caller allocates `out` (the reference
+ * allocated it, flash_api.cpp:542). */
+char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, const void *v,
+                          const int32_t *cu_seqlens_q, const int32_t *cu_seqlens_k, int batch,
+                          int total_q, int total_k, int num_heads, int num_heads_k,
+                          int head_size, int max_seqlen_q, int max_seqlen_k,
+                          int64_t q_tok_stride, int64_t q_head_stride, int64_t k_tok_stride,
+                          int64_t k_head_stride, int64_t v_tok_stride, int64_t v_head_stride,
+                          int64_t o_tok_stride, int64_t o_head_stride, float softmax_scale,
+                          int is_causal, int dtype, aici_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AICI_B200_H_ */

@@ -1,0 +1,155 @@
+"""GPU parity tests for decode attention over the paged cache (v1 and v2 entry points), through
+the C ABI, against the CPU oracle's fp32-softmax result.  Tolerance (stated by the benchmark
+definition): max-abs <= 2e-2 and mean-abs <= 2e-3 for bf16 outputs."""
+import pytest
+import torch
+
+from aici_b200 import _lib, tch_cuda, workloads
+from oracle import cpu_oracle as O
+
+pytestmark = pytest.mark.gpu
+MAX_ABS, MEAN_ABS = 2e-2, 2e-3
+
+
+def _case(seed, hq, hkv, ctx_list, nblk):
+    g = torch.Generator().manual_seed(seed)
+    kc = torch.randn(nblk, hkv, 16, 16, 8, generator=g).to(torch.bfloat16)
+    vc = torch.randn(nblk, hkv, 128, 16, generator=g).to(torch.bfloat16)
+    q = torch.randn(len(ctx_list), hq, 128, generator=g).to(torch.bfloat16)
+    table, _rows = workloads.build_block_tables(ctx_list, nblk, seed + 1)
+    return q, kc, vc, table, torch.tensor(ctx_list, dtype=torch.int32)
+
+
+def _run_v1(dev, q, kc, vc, hkv, scale, bt, cl):
+    out = torch.full(q.shape, float("nan"), dtype=torch.bfloat16, device=dev)
+    tch_cuda.paged_attention_v1(out, q.to(dev), kc.to(dev), vc.to(dev), hkv, scale, bt.to(dev),
+                                cl.to(dev), 16, int(cl.max()), None)
+    return out.cpu()
+
+
+def _check(got, want):
+    assert not torch.isnan(got.float()).any()
+    mx, mean = O.error_stats(got, want)
+    assert mx <= MAX_ABS and mean <= MEAN_ABS, (mx, mean)
+
+
+@pytest.mark.parametrize("hq,hkv", [(4, 4), (8, 2), (8, 1), (4, 2)])
+def test_edge_context_lengths(cuda_device, hq, hkv):
+    ctx = [1, 15, 16, 17, 255, 256, 257, 511, 512, 513, 1000, 0, 3]
+    q, kc, vc, bt, cl = _case(300 + hq * 10 + hkv, hq, hkv, ctx, 400)
+    scale = 1.0 / 128 ** 0.5
+    want = O.paged_attention_v1(q, kc, vc, hkv, scale, bt, cl)
+    got = _run_v1(cuda_device, q, kc, vc, hkv, scale, bt, cl)
+    _check(got, want)
+    assert float(got[ctx.index(0)].float().abs().max()) == 0.0
+    assert _lib.last_status() == 0
+
+
+def test_tail_block_garbage_is_ignored(cuda_device):
+    """Cache slots past context_len may hold NaN/Inf (attention_kernels.cu:317-326)."""
+    ctx = [5, 33, 250]
+    q, kc, vc, bt, cl = _case(311, 8, 2, ctx, 64)
+    for i, c in enumerate(ctx):
+        blk, off = int(bt[i, (c - 1) // 16]), (c - 1) % 16
+        kc[blk, :, :, off + 1:, :] = float("nan")
+        vc[blk, :, :, off + 1:] = float("inf")
+    scale = 0.09
+    want = O.paged_attention_v1(q, kc, vc, 2, scale, bt, cl)
+    _check(_run_v1(cuda_device, q, kc, vc, 2, scale, bt, cl), want)
+
+
+def test_strided_query_rows(cuda_device):
+    ctx = [40, 300]
+    q, kc, vc, bt, cl = _case(312, 8, 2, ctx, 64)
+    fused = torch.zeros(2, 3 * 8 * 128, dtype=torch.bfloat16)
+    fused[:, :8 * 128] = q.view(2, -1)
+    qd = fused.to(cuda_device)[:, :8 * 128].view(2, 8, 128)
+    out = torch.empty(2, 8, 128, dtype=torch.bfloat16, device=cuda_device)
+    tch_cuda.paged_attention_v1(out, qd, kc.to(cuda_device), vc.to(cuda_device), 2, 0.1,
+                                bt.to(cuda_device), cl.to(cuda_device), 16, 300, None)
+    _check(out.cpu(), O.paged_attention_v1(q, kc, vc, 2, 0.1, bt, cl))
+
+
+@pytest.mark.parametrize("chunk", [16, 64, 512])
+def test_chunk_sizes(cuda_device, chunk):
+    ctx = [700, 16, 1, 2049, 130]
+    q, kc, vc, bt, cl = _case(320, 8, 2, ctx, 300)
+    _lib.check("tune", _lib.lib().aici_tune_decode_chunk(chunk))
+    try:
+        got = _run_v1(cuda_device, q, kc, vc, 2, 0.088, bt, cl)
+    finally:
+        _lib.check("tune", _lib.lib().aici_tune_decode_chunk(0))
+    _check(got, O.paged_attention_v1(q, kc, vc, 2, 0.088, bt, cl))
+
+
+def test_v2_entry_point_and_its_temporaries(cuda_device):
+    ctx = [5, 512, 513, 1500, 2048]
+    hq, hkv = 8, 2
+    q, kc, vc, bt, cl = _case(330, hq, hkv, ctx, 400)
+    scale = 1.0 / 128 ** 0.5
+    parts = (max(ctx) + 511) // 512
+    dev = cuda_device
+    out = torch.empty(len(ctx), hq, 128, dtype=torch.bfloat16, device=dev)
+    exp_sums = torch.zeros(len(ctx), hq, parts, dtype=torch.float32, device=dev)
+    max_logits = torch.zeros(len(ctx), hq, parts, dtype=torch.float32, device=dev)
+    tmp_out = torch.zeros(len(ctx), hq, parts, 128, dtype=torch.bfloat16, device=dev)
+    tch_cuda.paged_attention_v2(out, exp_sums, max_logits, tmp_out, q.to(dev), kc.to(dev), vc.to(dev),
+                                hkv, scale, bt.to(dev), cl.to(dev), 16, max(ctx), None)
+    want = O.paged_attention_v2(q, kc, vc, hkv, scale, bt, cl, partition_size=512)
+    _check(out.cpu(), want)
+    # partition statistics carry the reference's meaning: recombining them on the host gives out
+    es, ml, to = exp_sums.cpu(), max_logits.cpu(), tmp_out.cpu().float()
+    for s, c in enumerate(ctx):
+        n = (c + 511) // 512
+        m = ml[s, :, :n].max(dim=1, keepdim=True).values
+        w = es[s, :, :n] * torch.exp(ml[s, :, :n] - m)
+        rec = (to[s, :, :n] * (w / (w.sum(1, keepdim=True) + 1e-6)).unsqueeze(-1)).sum(1)
+        mx, mean = O.error_stats(rec, want[s])
+        assert mx <= MAX_ABS and mean <= MEAN_ABS
+    assert _lib.last_status() == 0
+
+
+def test_bad_block_table_entry_is_recorded_not_trapped(cuda_device):
+    ctx = [20]
+    q, kc, vc, bt, cl = _case(340, 4, 4, ctx, 8)
+    bt[0, 1] = 8  # one past the pool
+    _run_v1(cuda_device, q, kc, vc, 4, 0.1, bt, cl)
+    assert _lib.last_status() & 1
+    assert _lib.last_status() == 0
+
+
+def test_rejects_unsupported_shapes(cuda_device):
+    dev = cuda_device
+    q = torch.zeros(1, 12, 128, dtype=torch.bfloat16, device=dev)
+    kc = torch.zeros(2, 4, 16, 16, 8, dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros(2, 4, 128, 16, dtype=torch.bfloat16, device=dev)
+    bt = torch.zeros(1, 1, dtype=torch.int32, device=dev)
+    cl = torch.ones(1, dtype=torch.int32, device=dev)
+    with pytest.raises(_lib.AiciError, match="must be 1, 2, 4 or 8"):
+        tch_cuda.paged_attention_v1(torch.empty_like(q), q, kc, vc, 4, 1.0, bt, cl, 16, 1, None)
+    with pytest.raises(_lib.AiciError, match="alibi"):
+        tch_cuda.paged_attention_v1(torch.empty_like(q), q, kc, vc, 4, 1.0, bt, cl, 16, 1,
+                                    torch.zeros(12, device=dev))
+
+
+@pytest.mark.parametrize("name", ["llama2_7b", "llama3_8b"])
+def test_benchmark_configs_full_size(cuda_device, name):
+    """Configs 2 and 3 at full size, checked against the oracle on every row, plus the
+    cache write of the new tokens (bit-exact on the touched blocks)."""
+    w = workloads.decode_llama2_7b(cuda_device) if name == "llama2_7b" else workloads.decode_llama3_8b(cuda_device)
+    tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
+    out = torch.empty_like(w.query)
+    tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                w.block_tables, w.context_lens, 16, w.max_context_len, None)
+    torch.cuda.synchronize()
+    assert _lib.last_status() == 0
+    kc, vc = w.key_cache.cpu(), w.value_cache.cpu()
+    # the written slots hold the new tokens
+    nk, nv, slots = w.new_key.cpu(), w.new_value.cpu(), w.slot_mapping.cpu()
+    kg, vg = torch.zeros_like(nk), torch.zeros_like(nv)
+    O.gather_cached_kv(kg, vg, kc, vc, slots)
+    assert torch.equal(kg.view(torch.int16), nk.view(torch.int16))
+    assert torch.equal(vg.view(torch.int16), nv.view(torch.int16))
+    want = O.paged_attention_v1(w.query.cpu(), kc, vc, w.num_kv_heads, w.scale, w.block_tables.cpu(),
+                                w.context_lens.cpu())
+    _check(out.cpu(), want)

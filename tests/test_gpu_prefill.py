@@ -1,0 +1,125 @@
+"""GPU parity tests for variable-length causal prefill attention, through the C ABI, against
+the CPU oracle's fp32-softmax result.  Tolerance: max-abs <= 2e-2, mean-abs <= 2e-3 (bf16)."""
+import pytest
+import torch
+
+from aici_b200 import _lib, tch_cuda, workloads
+from oracle import cpu_oracle as O
+
+pytestmark = pytest.mark.gpu
+MAX_ABS, MEAN_ABS = 2e-2, 2e-3
+
+
+def _run(dev, w, causal=True):
+    return tch_cuda.flash_attn_varlen(w.q, w.k, w.v, w.cu_seqlens_q, w.cu_seqlens_k, w.max_seqlen_q,
+                                      w.max_seqlen_k, w.scale, causal)
+
+
+def _check_full(w, out, causal=True):
+    want = O.flash_attn_varlen(w.q.cpu(), w.k.cpu(), w.v.cpu(), w.cu_seqlens_q.cpu(), w.cu_seqlens_k.cpu(),
+                               w.max_seqlen_q, w.max_seqlen_k, w.scale, causal)
+    got = out.cpu()
+    assert not torch.isnan(got.float()).any()
+    mx, mean = O.error_stats(got, want)
+    assert mx <= MAX_ABS and mean <= MEAN_ABS, (mx, mean)
+    return want
+
+
+def test_config1_small_varlen(cuda_device):
+    w = workloads.prefill_small(cuda_device)
+    out = _run(cuda_device, w)
+    _check_full(w, out)
+    assert _lib.last_status() == 0
+
+
+@pytest.mark.parametrize("lens_q,lens_k,hq,hkv", [
+    ([1, 127, 128, 129, 300], [1, 127, 128, 129, 300], 4, 4),   # ragged tails around the tile size
+    ([5, 1, 40, 130], [70, 333, 40, 400], 8, 2),                # chunked prefill: k_len > q_len
+    ([200, 40], [72, 8], 4, 1),                                 # k_len < q_len: leading rows see nothing
+    ([512] * 3, [1536] * 3, 8, 2),                              # config-5 variant with 1024 cached tokens
+])
+def test_ragged_and_bottom_right_mask(cuda_device, lens_q, lens_k, hq, hkv):
+    w = workloads.make_prefill("t", cuda_device, lens_q=lens_q, lens_k=lens_k, num_heads=hq,
+                               num_kv_heads=hkv, seed=77)
+    out = _run(cuda_device, w)
+    want = _check_full(w, out)
+    if lens_k[0] < lens_q[0]:
+        assert float(out[:lens_q[0] - lens_k[0]].float().abs().max()) == 0.0
+        assert float(want[:lens_q[0] - lens_k[0]].abs().max()) == 0.0
+    assert _lib.last_status() == 0
+
+
+def test_non_causal(cuda_device):
+    w = workloads.make_prefill("t", cuda_device, lens_q=[100, 260], lens_k=[150, 260], num_heads=4,
+                               num_kv_heads=2, seed=78)
+    _check_full(w, _run(cuda_device, w, causal=False), causal=False)
+
+
+def test_strided_inputs_from_fused_qkv(cuda_device):
+    g = torch.Generator(device=cuda_device).manual_seed(79)
+    n, hq, hkv, d = 333, 8, 2, 128
+    qkv = workloads.randn_bf16((n, (hq + 2 * hkv) * d), cuda_device, g)
+    q = qkv[:, :hq * d].view(n, hq, d)
+    k = qkv[:, hq * d:(hq + hkv) * d].view(n, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].view(n, hkv, d)
+    cu = torch.tensor([0, 100, 333], dtype=torch.int32, device=cuda_device)
+    out = tch_cuda.flash_attn_varlen(q, k, v, cu, cu, 233, 233, 0.09, True)
+    want = O.flash_attn_varlen(q.cpu(), k.cpu(), v.cpu(), cu.cpu(), cu.cpu(), 233, 233, 0.09, True)
+    mx, mean = O.error_stats(out.cpu(), want)
+    assert mx <= MAX_ABS and mean <= MEAN_ABS, (mx, mean)
+
+
+def test_large_scores_exercise_the_lazy_rescale(cuda_device):
+    """Scores that keep growing along the key axis force the running maximum to move by more
+    than the rescale threshold many times."""
+    n, hq = 1024, 2
+    g = torch.Generator(device=cuda_device).manual_seed(80)
+    q = workloads.randn_bf16((n, hq, 128), cuda_device, g)
+    k = workloads.randn_bf16((n, hq, 128), cuda_device, g)
+    v = workloads.randn_bf16((n, hq, 128), cuda_device, g)
+    ramp = torch.linspace(0.2, 3.0, n, device=cuda_device).view(n, 1, 1)
+    k = (k * ramp).to(torch.bfloat16)
+    cu = torch.tensor([0, n], dtype=torch.int32, device=cuda_device)
+    out = tch_cuda.flash_attn_varlen(q, k, v, cu, cu, n, n, 0.5, True)
+    want = O.flash_attn_varlen(q.cpu(), k.cpu(), v.cpu(), cu.cpu(), cu.cpu(), n, n, 0.5, True)
+    mx, mean = O.error_stats(out.cpu(), want)
+    assert mx <= 4e-2 and mean <= MEAN_ABS, (mx, mean)  # peaked softmax: |out| up to ~4, bf16 ulp 1.6e-2
+
+
+def test_mixed_step_prefill_chunks(cuda_device):
+    w = workloads.prefill_mixed_chunks(cuda_device)
+    _check_full(w, _run(cuda_device, w))
+
+
+def test_long_context_sampled_rows(cuda_device):
+    """Config 4 shape at a length the CPU can check by rows: 2 x 8192, 64 q / 8 kv heads; all
+    rows of the first and last query tile of each sequence for two heads plus random rows."""
+    w = workloads.prefill_long(cuda_device, seqlen=8192)
+    out = _run(cuda_device, w)
+    torch.cuda.synchronize()
+    assert _lib.last_status() == 0
+    g = torch.Generator().manual_seed(81)
+    rows = []
+    for s in range(2):
+        base = s * 8192
+        for h in (0, 63):
+            rows += [[s, base + r, h] for r in list(range(128)) + list(range(8192 - 128, 8192))]
+    rnd_tok = torch.randint(0, 2 * 8192, (1024,), generator=g)
+    rnd_head = torch.randint(0, 64, (1024,), generator=g)
+    rows += [[int(t) // 8192, int(t), int(h)] for t, h in zip(rnd_tok, rnd_head)]
+    rows = torch.tensor(rows, dtype=torch.int32)
+    want = O.flash_attn_varlen_rows(w.q.cpu(), w.k.cpu(), w.v.cpu(), w.cu_seqlens_q.cpu(),
+                                    w.cu_seqlens_k.cpu(), rows, w.scale, True)
+    got = out.cpu()[rows[:, 1].long(), rows[:, 2].long()]
+    mx, mean = O.error_stats(got, want)
+    assert mx <= MAX_ABS and mean <= MEAN_ABS, (mx, mean)
+
+
+def test_rejects_unsupported(cuda_device):
+    q = torch.zeros(4, 2, 64, dtype=torch.bfloat16, device=cuda_device)
+    cu = torch.tensor([0, 4], dtype=torch.int32, device=cuda_device)
+    with pytest.raises(_lib.AiciError, match="head_size must be 128"):
+        tch_cuda.flash_attn_varlen(q, q, q, cu, cu, 4, 4, 1.0, True)
+    q = torch.zeros(4, 2, 128, dtype=torch.float16, device=cuda_device)
+    with pytest.raises(_lib.AiciError, match="bf16"):
+        tch_cuda.flash_attn_varlen(q, q, q, cu, cu, 4, 4, 1.0, True)
