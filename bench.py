@@ -1,0 +1,392 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decode step of the Llama-2-7B-shaped paged workload (batch 64, 32 MHA heads,
+head size 128, block size 16, contexts uniform in [512, 4096], 16384-block pool): the cache
+write of the 64 new tokens (reshape_and_cache) followed by decode attention over the paged
+cache (paged_attention_v1).  With N > 1 the KV heads are split over the ranks (tensor-parallel
+layout) and the head outputs are all-gathered over NCCL inside the step, so the total work is
+fixed ("strong" scaling).  The metric is the achieved HBM traffic rate in TB/s computed from
+the ALGORITHMIC bytes of the step (K and V once per (sequence, kv head), q, out, block tables,
+context lengths, and the cache write), aggregated over all ranks.
+
+The line also carries the long-context causal prefill throughput (2 x 32768 tokens, 64 q / 8 kv
+heads) in TFLOP/s under "prefill", the roofline of the dominant decode kernel, an end-to-end
+figure through the public API with host buffers, and the CPU baseline: the PyTorch-CPU port of
+rLLM's own CPU kernels timed on a bounded sample of the same workload.
+
+--impl reference times that CPU port (the reference's CPU path for this operation; its Rust
+original cannot be built in this image) with all host threads, on rank 0 only.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "paged-decode attn HBM TB/s (prefill attn TFLOPS under 'prefill')"
+UNIT = "TB/s"
+WORKLOAD = "decode_llama2_7b_b64_mha32_d128_bs16_ctx512-4096_pool16384+reshape_and_cache_64"
+CPU_SAMPLE_SEQS = 8
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
+
+    def __init__(self, index, period=0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                r = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop_evt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the PyTorch-CPU port of rLLM's CPU kernels on a bounded sample of the workload
+# ---------------------------------------------------------------------------------------------
+def cpu_sample_inputs(n_seqs):
+    """The first n_seqs sequences of the decode workload with their blocks compacted into a small
+    fp32 pool (the CPU build of rLLM runs fp32).  Contexts and tables are the benchmark's own."""
+    from aici_b200 import workloads
+    ctx = workloads.draw_context_lens("uniform", 64, 512, 4096, 2001)[:n_seqs]
+    hkv = hq = 32
+    nblk = sum((c + 15) // 16 for c in ctx)
+    g = torch.Generator().manual_seed(2003)
+    kc = torch.randn(nblk, hkv, 16, 16, 8, generator=g)
+    vc = torch.randn(nblk, hkv, 128, 16, generator=g)
+    q = torch.randn(n_seqs, hq, 128, generator=g)
+    table, _ = workloads.build_block_tables(ctx, nblk, 2002)
+    nk = torch.randn(n_seqs, hkv, 128, generator=g)
+    nv = torch.randn(n_seqs, hkv, 128, generator=g)
+    slots = torch.tensor([int(table[i, (c - 1) // 16]) * 16 + (c - 1) % 16 for i, c in enumerate(ctx)],
+                         dtype=torch.int32)
+    kv = sum(ctx) * 2 * hkv * 128 * 2
+    qo = n_seqs * hq * 128 * 2 * 2
+    bt = sum((c + 15) // 16 for c in ctx) * 4 + 4 * n_seqs
+    cw = n_seqs * hkv * 128 * 2 * 2 * 2
+    return dict(q=q, kc=kc, vc=vc, table=table, ctx=torch.tensor(ctx, dtype=torch.int32), nk=nk, nv=nv,
+                slots=slots, hkv=hkv, bytes=kv + qo + bt + cw)
+
+
+def cpu_step(c):
+    from oracle import refkernels_cpu as R
+    R.reshape_and_cache(c["nk"], c["nv"], c["kc"], c["vc"], c["slots"])
+    return R.decode_step_cpu(c["q"], c["kc"], c["vc"], c["hkv"], 1.0 / 128 ** 0.5, c["table"], c["ctx"], 16)
+
+
+def time_cpu(steps, warmup):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    c = cpu_sample_inputs(CPU_SAMPLE_SEQS)
+    for _ in range(warmup):
+        cpu_step(c)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(c)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return {"value": c["bytes"] / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": "first %d of the 64 sequences (%.1f MB algorithmic), fp32, gather_cached_kv + "
+                      "repeat_kv + per-sequence scaled_dot_product_attention as in refkernels.rs, "
+                      "%.3f s per step" % (CPU_SAMPLE_SEQS, c["bytes"] / 1e6, dt)}, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warm = max(1, args.steps), max(1, args.warmup)
+    cb, dt = time_cpu(steps, warm)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "CPU path of the reference (refkernels.rs port), bounded sample"},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+    from aici_b200 import tch_cuda, workloads, _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node %d" % args.gpus)
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    shard = workloads.Shard(rank=rank, world=world)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- decode workload ------------------------------------------------------------------
+    w = workloads.decode_llama2_7b(dev, shard=shard)
+    S, hq_local = w.query.shape[0], w.query.shape[1]
+    out = torch.empty_like(w.query)
+    gathered = torch.empty(world, S, hq_local, 128, dtype=torch.bfloat16, device=dev) if world > 1 else None
+    step_bytes_local = w.algorithmic_bytes() + w.cache_write_bytes()
+    decode_bytes_local = w.algorithmic_bytes()
+
+    def step():
+        tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
+        tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                    w.block_tables, w.context_lens, 16, w.max_context_len, None)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    att_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+              for _ in range(args.steps)]
+    ev0.record()
+    for i in range(args.steps):
+        tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
+        att_ev[i][0].record()
+        tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                    w.block_tables, w.context_lens, 16, w.max_context_len, None)
+        att_ev[i][1].record()
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+    ev1.record()
+    barrier()
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    ms_step = ms_total / args.steps
+    att_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in att_ev) / args.steps)
+    status = _lib.last_status()
+    if status != 0:
+        raise SystemExit("device status word is %d after the timed region" % status)
+    value = step_bytes_local * world / (ms_step * 1e-3) / 1e12
+    achieved_gbs = decode_bytes_local / (att_ms * 1e-3) / 1e9
+
+    # ---- end to end through the public API with host buffers -------------------------------
+    host = {
+        "q": w.query.cpu().pin_memory(), "nk": w.new_key.cpu().pin_memory(), "nv": w.new_value.cpu().pin_memory(),
+        "slots": w.slot_mapping.cpu().pin_memory(), "bt": w.block_tables.cpu().pin_memory(),
+        "cl": w.context_lens.cpu().pin_memory(),
+    }
+    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step():
+        d = {k: t.to(dev, non_blocking=True) for k, t in host.items()}
+        tch_cuda.reshape_and_cache(d["nk"], d["nv"], w.key_cache, w.value_cache, d["slots"])
+        o = torch.empty_like(d["q"])
+        tch_cuda.paged_attention_v1(o, d["q"], w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                    d["bt"], d["cl"], 16, w.max_context_len, None)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, o)
+        host_out.copy_(o, non_blocking=True)
+
+    for _ in range(max(3, args.warmup // 2)):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    ev0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    ev1.record()
+    barrier()
+    e2e_ms = max_over_ranks(max(ev0.elapsed_time(ev1), (time.perf_counter() - t0) * 1e3)) / args.steps
+    e2e_value = step_bytes_local * world / (e2e_ms * 1e-3) / 1e12
+
+    # ---- long-context causal prefill (2 x 32768, 64 q / 8 kv heads; heads split over ranks) ---
+    del w.key_cache, w.value_cache
+    torch.cuda.empty_cache()
+    pw = workloads.prefill_long(dev, shard=shard)
+    p_steps, p_warm = max(2, min(args.steps, 5)), 3
+
+    def pstep():
+        return tch_cuda.flash_attn_varlen(pw.q, pw.k, pw.v, pw.cu_seqlens_q, pw.cu_seqlens_k,
+                                          pw.max_seqlen_q, pw.max_seqlen_k, pw.scale, True)
+
+    pg = None
+    if world > 1:
+        pg = torch.empty(world, pw.q.shape[0], pw.q.shape[1], 128, dtype=torch.bfloat16, device=dev)
+    for _ in range(p_warm):
+        o = pstep()
+        if world > 1:
+            dist.all_gather_into_tensor(pg, o)
+    barrier()
+    k_ms = []
+    ev0.record()
+    for _ in range(p_steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        o = pstep()
+        b.record()
+        k_ms.append((a, b))
+        if world > 1:
+            dist.all_gather_into_tensor(pg, o)
+    ev1.record()
+    barrier()
+    p_ms = max_over_ranks(ev0.elapsed_time(ev1)) / p_steps
+    p_kernel_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in k_ms) / p_steps)
+    clocks = sampler.stop()
+    p_flops_local = pw.flops()
+    p_tflops = p_flops_local * world / (p_ms * 1e-3) / 1e12
+    p_kernel_tflops = p_flops_local / (p_kernel_ms * 1e-3) / 1e12
+    status = _lib.last_status()
+    if status != 0:
+        raise SystemExit("device status word is %d after the prefill region" % status)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu_baseline, _ = time_cpu(steps=8, warmup=1)
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "workload": WORKLOAD, "sharding": "kv-heads/%d" % world,
+            "l2": "no flush: each step streams %.2f GB of K/V per GPU, far above the 126 MB L2" % (
+                decode_bytes_local / 1e9),
+            "algorithmic_bytes_per_step": step_bytes_local * world,
+            "collective": "nccl all_gather of head outputs" if world > 1 else "none",
+        },
+        "roofline": {
+            "kernel": "paged_decode_kernel (+ plan and merge launches of the same call)",
+            "bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": achieved_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
+            "launch_ms": att_ms, "traffic": None,
+        },
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h,
+                "note": "q, new k/v, slot map, block tables, context lens copied from pinned host memory "
+                        "and the output read back every step; the KV cache is resident state"},
+        "gpu_launches": 4 * args.steps,
+        "clocks": clocks,
+        "prefill": {
+            "workload": pw.name + "_causal_d128", "tflops": p_tflops, "ms_per_step": p_ms, "steps": p_steps,
+            "flops_per_step": p_flops_local * world,
+            "roofline": {"kernel": "varlen_prefill_kernel", "bound": "tensor", "achieved": p_kernel_tflops,
+                         "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                         "frac": p_kernel_tflops / peaks["bf16_tflops_sustained"],
+                         "frac_of_burst_peak": p_kernel_tflops / peaks["bf16_tflops"],
+                         "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "launch_ms": p_kernel_ms,
+                         "traffic": None},
+        },
+    }
+    if cpu_baseline is not None:
+        line["cpu_baseline"] = cpu_baseline
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
