@@ -21,6 +21,7 @@ EXPORTS = (
     "aici_paged_attention_workspace_bytes",
     "aici_paged_attention_v1",
     "aici_paged_attention_v2",
+    "aici_paged_attention_v1_static",
     "aici_mha_varlen_fwd",
 )
 

@@ -613,3 +613,58 @@ extern "C" char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_
   p.status = st;
   return launch_decode<__nv_bfloat16>(p, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
+
+// ---- decode attention for callers that cannot provide scratch memory ------------------------------
+//
+// aici_paged_attention_v1 needs a workspace for its chunk list and split-context partials, and
+// somebody has to allocate it.  Two kinds of caller cannot: a serving loop whose KV-cache pool was
+// sized to take (nearly) all free device memory after start-up profiling, so that a later
+// allocation can fail or stall the step; and a binding from a runtime that has no device
+// allocator of its own (the Rust crate once libtorch is out of the call path).  For them the
+// library carries the workspace itself: a fixed array in device memory that exists on every GPU
+// that loads the library, from load to exit.
+//
+// Rules that follow from sharing one array:
+//   * sizes whose workspace would exceed kStaticScratchBytes are refused with an error string;
+//   * the array keeps whatever the previous call left; nothing in it has to start at zero (the
+//     plan kernel writes the chunk count and list, every partial is written before it is read),
+//     so no clearing pass runs;
+//   * two calls that overlap on the GPU (different streams, or different threads on one device)
+//     race on the array -- serialise them on one stream;
+//   * the first call on each device looks the array's device address up (the name used in host
+//     code is only a handle, not an address a kernel could use) and sets a function attribute;
+//     make that first call outside any stream capture.
+constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB: config 2 (64 x 32 heads x 4096 ctx) needs 17 MiB
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+extern "C" char *aici_paged_attention_v1_static(
+    void *out, const void *query, const void *key_cache, const void *value_cache, int num_kv_heads,
+    float scale, const int32_t *block_tables, const int32_t *context_lens, int block_size,
+    int max_context_len, const float *alibi_slopes, int num_seqs, int num_heads, int head_size,
+    int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_stride, int64_t kv_block_stride,
+    int64_t kv_head_stride, int dtype, aici_stream_t stream) {
+  const char *fn = "aici_paged_attention_v1_static";
+  static void *scratch_addr[64] = {nullptr};
+  int dev = 0;
+  AICI_CUDA(cudaGetDevice(&dev));
+  AICI_CHECK(dev >= 0 && dev < 64, "%s: device index %d out of range", fn, dev);
+  if (scratch_addr[dev] == nullptr) {
+    void *p = nullptr;
+    AICI_CUDA(cudaGetSymbolAddress(&p, g_decode_scratch));
+    AICI_CHECK(p != nullptr, "%s: the scratch array has no device address", fn);
+    scratch_addr[dev] = p;
+  }
+  if (num_seqs > 0 && num_heads > 0) {
+    const size_t need = aici_paged_attention_workspace_bytes(num_seqs, num_heads, max_context_len);
+    AICI_CHECK(need <= kStaticScratchBytes,
+               "%s: this batch needs %zu bytes of scratch but the built-in array holds %zu "
+               "(num_seqs * ceil(max_context_len / chunk) * num_heads is too large); use "
+               "aici_paged_attention_v1 with a caller-owned workspace",
+               fn, need, kStaticScratchBytes);
+  }
+  return aici_paged_attention_v1(out, query, key_cache, value_cache, num_kv_heads, scale, block_tables,
+                                 context_lens, block_size, max_context_len, alibi_slopes, num_seqs,
+                                 num_heads, head_size, max_num_blocks_per_seq, num_blocks, q_stride,
+                                 kv_block_stride, kv_head_stride, scratch_addr[dev], kStaticScratchBytes,
+                                 dtype, stream);
+}

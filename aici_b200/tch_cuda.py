@@ -329,3 +329,28 @@ def paged_attention_v2(out: torch.Tensor, exp_sums: torch.Tensor, max_logits: to
             ctypes.c_int64(query.stride(0)), ctypes.c_int64(key_cache.stride(0)),
             ctypes.c_int64(key_cache.stride(1)), ctypes.c_int(_dtype(fn, query)), _stream(dev))
     _lib.check(fn, res)
+
+
+def paged_attention_v1_static(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tensor,
+                              value_cache: torch.Tensor, num_kv_heads: int, scale: float,
+                              block_tables: torch.Tensor, context_lens: torch.Tensor, block_size: int,
+                              max_context_len: int, alibi_slopes: Optional[torch.Tensor]) -> None:
+    """paged_attention_v1 for callers that must not allocate at call time: no workspace tensor is
+    created here and the library allocates nothing; the scratch is a 32 MiB array inside the
+    library.  Larger batches raise.  Calls on one device must not overlap (keep one stream)."""
+    fn = "paged_attention_v1_static"
+    if alibi_slopes is not None:
+        raise AiciError("%s: alibi_slopes is not supported" % fn)
+    dev, num_blocks, head_size = _decode_common(fn, out, query, key_cache, value_cache,
+                                                num_kv_heads, block_tables, context_lens, block_size)
+    num_seqs, num_heads, _ = query.shape
+    with torch.cuda.device(dev):
+        res = _lib.lib().aici_paged_attention_v1_static(
+            _p(out), _p(query), _p(key_cache), _p(value_cache), ctypes.c_int(num_kv_heads),
+            ctypes.c_float(scale), _p(block_tables), _p(context_lens), ctypes.c_int(block_size),
+            ctypes.c_int(int(max_context_len)), ctypes.c_void_p(0), ctypes.c_int(num_seqs),
+            ctypes.c_int(num_heads), ctypes.c_int(head_size), ctypes.c_int(block_tables.shape[1]),
+            ctypes.c_int64(num_blocks), ctypes.c_int64(query.stride(0)),
+            ctypes.c_int64(key_cache.stride(0)), ctypes.c_int64(key_cache.stride(1)),
+            ctypes.c_int(_dtype(fn, query)), _stream(dev))
+    _lib.check(fn, res)

@@ -124,6 +124,24 @@ char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_logits, voi
                               int64_t kv_block_stride, int64_t kv_head_stride, int dtype,
                               aici_stream_t stream);
 
+/* Same operation and arguments as aici_paged_attention_v1 without the workspace: the scratch
+ * lives in a 32 MiB array built into the library (present on every GPU that loads it).  This
+ * entry point has no counterpart in the reference.  It is meant for callers that must not
+ * allocate device memory at call time -- a serving loop that gave all spare memory to the KV
+ * pool, or a binding without a device allocator -- and it calls no allocation routine itself.
+ * Batches whose workspace (aici_paged_attention_workspace_bytes) exceeds 32 MiB are refused with
+ * an error string.  All calls on one device share the array: calls that overlap on the GPU race,
+ * so keep them on one stream.  The first call on a device looks up the array's address; make it
+ * outside any stream capture. */
+char *aici_paged_attention_v1_static(void *out, const void *query, const void *key_cache,
+                                     const void *value_cache, int num_kv_heads, float scale,
+                                     const int32_t *block_tables, const int32_t *context_lens,
+                                     int block_size, int max_context_len,
+                                     const float *alibi_slopes, int num_seqs, int num_heads,
+                                     int head_size, int max_num_blocks_per_seq, int64_t num_blocks,
+                                     int64_t q_stride, int64_t kv_block_stride,
+                                     int64_t kv_head_stride, int dtype, aici_stream_t stream);
+
 /* ---- variable-length causal prefill attention --------------------------------------- */
 
 /* Replaces mha_varlen_fwd_C (lib.rs:29-47; kernels/flash_attn/flash_api.cpp:622-655,
