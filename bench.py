@@ -373,6 +373,30 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_profile_case(args):
+    """Small single-GPU cases for profiler captures (a few hundred MB, three launches): the
+    numbers printed here are not benchmark values."""
+    from aici_b200 import tch_cuda, workloads
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if args.profile == "decode":
+        w = workloads.decode_llama2_7b(dev, num_seqs=16, pool_blocks=4096)
+        out = torch.empty_like(w.query)
+        for _ in range(3):
+            tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
+            tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                        w.block_tables, w.context_lens, 16, w.max_context_len, None)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_case": "decode", "seqs": 16, "algorithmic_bytes": w.algorithmic_bytes()}))
+    else:
+        pw = workloads.prefill_long(dev, seqlen=4096)
+        for _ in range(3):
+            tch_cuda.flash_attn_varlen(pw.q, pw.k, pw.v, pw.cu_seqlens_q, pw.cu_seqlens_k, pw.max_seqlen_q,
+                                       pw.max_seqlen_k, pw.scale, True)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_case": "prefill", "seqlen": 4096, "flops": pw.flops()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -380,7 +404,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
+                    help="run a small case three times for a profiler capture and exit")
     args = ap.parse_args()
+    if args.profile:
+        run_profile_case(args)
+        return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
