@@ -38,6 +38,10 @@ METRIC = "paged-decode attn HBM TB/s (prefill attn TFLOPS under 'prefill')"
 UNIT = "TB/s"
 WORKLOAD = "decode_llama2_7b_b64_mha32_d128_bs16_ctx512-4096_pool16384+reshape_and_cache_64"
 CPU_SAMPLE_SEQS = 8
+# DRAM bytes (read + write) of paged_decode_kernel per algorithmic byte, from the ncu capture of
+# the 16-sequence case summarised in profiles/paged_decode_kernel_llama2_7b_16seq.md; traffic
+# grows in proportion to the tokens read, so the ratio carries over to the full launch.
+DECODE_TRAFFIC_RATIO = 1.016
 
 
 def load_peaks():
@@ -347,7 +351,9 @@ def run_ours(args):
             "kernel": "paged_decode_kernel (+ plan and merge launches of the same call)",
             "bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": achieved_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
-            "launch_ms": att_ms, "traffic": None,
+            "launch_ms": att_ms,
+            "traffic": DECODE_TRAFFIC_RATIO * decode_bytes_local,
+            "traffic_note": "ncu dram read+write of a 16-sequence launch scaled by bytes (profiles/)",
         },
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h,
