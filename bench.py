@@ -225,7 +225,7 @@ def run_ours(args):
         tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
                                     w.block_tables, w.context_lens, 16, w.max_context_len, None)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
+            dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), out)
 
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
@@ -243,7 +243,7 @@ def run_ours(args):
                                     w.block_tables, w.context_lens, 16, w.max_context_len, None)
         att_ev[i][1].record()
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
+            dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), out)
     ev1.record()
     barrier()
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
@@ -272,7 +272,7 @@ def run_ours(args):
         tch_cuda.paged_attention_v1(o, d["q"], w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
                                     d["bt"], d["cl"], 16, w.max_context_len, None)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, o)
+            dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), o)
         host_out.copy_(o, non_blocking=True)
 
     for _ in range(max(3, args.warmup // 2)):
@@ -303,7 +303,7 @@ def run_ours(args):
     for _ in range(p_warm):
         o = pstep()
         if world > 1:
-            dist.all_gather_into_tensor(pg, o)
+            dist.all_gather_into_tensor(pg.view(-1, pg.shape[2], 128), o)
     barrier()
     k_ms = []
     ev0.record()
@@ -314,7 +314,7 @@ def run_ours(args):
         b.record()
         k_ms.append((a, b))
         if world > 1:
-            dist.all_gather_into_tensor(pg, o)
+            dist.all_gather_into_tensor(pg.view(-1, pg.shape[2], 128), o)
     ev1.record()
     barrier()
     p_ms = max_over_ranks(ev0.elapsed_time(ev1)) / p_steps
