@@ -379,6 +379,148 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+
+# ---------------------------------------------------------------------------------------------
+# --suite: device timings of all five configurations at the current world size (no oracle here;
+# parity at every GPU count is covered by tests/test_gpu_multi.py)
+# ---------------------------------------------------------------------------------------------
+def run_suite(args):
+    import torch.distributed as dist
+    from aici_b200 import tch_cuda, workloads, _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    shard = workloads.Shard(rank=rank, world=world)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)  # 4x the L2
+    iters, warm = max(5, min(args.steps, 20)), 3
+    rows = []
+
+    def reduce_max(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, gather_fn=None):
+        """median device time of fn over `iters` launches, L2 flushed before each; max over ranks"""
+        ks, gs = [], []
+        for i in range(warm + iters):
+            flush.zero_()
+            a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            if world > 1:
+                dist.barrier()
+            a.record()
+            o = fn()
+            b.record()
+            if gather_fn is not None and world > 1:
+                gather_fn(o)
+            c.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                ks.append(a.elapsed_time(b))
+                gs.append(b.elapsed_time(c))
+        return reduce_max(statistics.median(ks)), reduce_max(statistics.median(gs))
+
+    def add(name, kind, work_local, k_ms, g_ms, extra=None):
+        total = work_local * world
+        if kind == "hbm":
+            ach = work_local / (k_ms * 1e-3) / 1e9
+            peak, unit = peaks["hbm_gbs"], "GB/s"
+        else:
+            ach = work_local / (k_ms * 1e-3) / 1e12
+            peak, unit = peaks["bf16_tflops_sustained"], "TFLOP/s"
+        row = {"config": name, "n_gpus": world, "kernel_ms": k_ms, "gather_ms": g_ms,
+               "work_per_gpu": work_local, "work_total": total, "achieved_per_gpu": ach, "unit": unit,
+               "frac_of_peak": ach / peak, "aggregate": ach * world,
+               "aggregate_with_gather": work_local * world / ((k_ms + g_ms) * 1e-3) / (1e9 if kind == "hbm" else 1e12)}
+        if extra:
+            row.update(extra)
+        rows.append(row)
+
+    def gather_into(buf):
+        def g(o):
+            dist.all_gather_into_tensor(buf.view(-1, o.shape[1], 128), o)
+        return g
+
+    # config 1: small varlen prefill
+    pw = workloads.prefill_small(dev, shard=shard)
+    buf = torch.empty(world, *pw.q.shape, dtype=torch.bfloat16, device=dev)
+    k_ms, g_ms = timed(lambda: tch_cuda.flash_attn_varlen(pw.q, pw.k, pw.v, pw.cu_seqlens_q, pw.cu_seqlens_k,
+                                                          pw.max_seqlen_q, pw.max_seqlen_k, pw.scale, True),
+                       gather_into(buf))
+    add("1 " + pw.name, "tensor", pw.flops(), k_ms, g_ms)
+    del pw, buf
+
+    # configs 2, 3, 5(decode)
+    for label, make in (("2", workloads.decode_llama2_7b), ("3", workloads.decode_llama3_8b),
+                        ("5-decode", workloads.decode_mixed_step)):
+        w = make(dev, shard=shard)
+        out = torch.empty_like(w.query)
+        buf = torch.empty(world, *w.query.shape, dtype=torch.bfloat16, device=dev)
+
+        def dec(w=w, out=out):
+            tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                        w.block_tables, w.context_lens, 16, w.max_context_len, None)
+            return out
+        k_ms, g_ms = timed(dec, gather_into(buf))
+        r_ms, _ = timed(lambda w=w: tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache,
+                                                               w.value_cache, w.slot_mapping))
+        add(label + " " + w.name, "hbm", w.algorithmic_bytes(), k_ms, g_ms,
+            {"reshape_and_cache_ms": r_ms, "max_context_len": w.max_context_len})
+        if label == "5-decode":
+            # fork copy, bandwidth variant: every block of the first 8 sequences to 4 children
+            used = set(w.block_tables.cpu().flatten().tolist())
+            free = [b for b in range(w.key_cache.shape[0]) if b not in used]
+            rows_ = [w.block_tables[i, :(c + 15) // 16].tolist() for i, c in enumerate(w.context_list)]
+            mapping = workloads.fork_block_mapping(rows_, 8, 4, free, whole_sequence=True)
+            pairs = sum(len(v) for v in mapping.values())
+            c_ms, _ = timed(lambda: tch_cuda.copy_blocks([w.key_cache], [w.value_cache], mapping))
+            blk_bytes = w.num_kv_heads * 128 * 16 * 2
+            add("5-copy_blocks whole-sequence fork (%d pairs, 1 layer)" % pairs, "hbm",
+                pairs * 2 * blk_bytes * 2, c_ms, 0.0)
+            last = workloads.fork_block_mapping(rows_, 32, 4, free)
+            c2_ms, _ = timed(lambda: tch_cuda.copy_blocks([w.key_cache] * 4, [w.value_cache] * 4, last))
+            add("5-copy_blocks last-block fork (128 pairs, 4 layers)", "hbm", 128 * 4 * 2 * blk_bytes * 2, c2_ms, 0.0)
+        del w, out, buf
+        torch.cuda.empty_cache()
+
+    # config 5 prefill part and its cache write (4288 tokens)
+    pw = workloads.prefill_mixed_chunks(dev, shard=shard)
+    buf = torch.empty(world, *pw.q.shape, dtype=torch.bfloat16, device=dev)
+    k_ms, g_ms = timed(lambda: tch_cuda.flash_attn_varlen(pw.q, pw.k, pw.v, pw.cu_seqlens_q, pw.cu_seqlens_k,
+                                                          pw.max_seqlen_q, pw.max_seqlen_k, pw.scale, True),
+                       gather_into(buf))
+    add("5-prefill " + pw.name, "tensor", pw.flops(), k_ms, g_ms)
+    hkv = pw.k.shape[1]
+    kc = torch.zeros(4288 // 16 + 8, hkv, 16, 16, 8, dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros(4288 // 16 + 8, hkv, 128, 16, dtype=torch.bfloat16, device=dev)
+    kk = torch.cat([pw.k, pw.k[:192]]).contiguous()
+    slots = torch.arange(4288, dtype=torch.int32, device=dev) + 5
+    r_ms, _ = timed(lambda: tch_cuda.reshape_and_cache(kk, kk, kc, vc, slots))
+    add("5-reshape_and_cache 4288 tokens", "hbm", 4288 * hkv * 128 * 2 * 2 * 2, r_ms, 0.0)
+    del pw, buf, kc, vc, kk
+
+    # config 4: long prefill
+    pw = workloads.prefill_long(dev, shard=shard)
+    buf = torch.empty(world, *pw.q.shape, dtype=torch.bfloat16, device=dev)
+    k_ms, g_ms = timed(lambda: tch_cuda.flash_attn_varlen(pw.q, pw.k, pw.v, pw.cu_seqlens_q, pw.cu_seqlens_k,
+                                                          pw.max_seqlen_q, pw.max_seqlen_k, pw.scale, True),
+                       gather_into(buf))
+    add("4 " + pw.name, "tensor", pw.flops(), k_ms, g_ms, {"frac_of_burst_peak": pw.flops() / (k_ms * 1e-3) / 1e12 / peaks["bf16_tflops"]})
+    status = _lib.last_status()
+    if rank == 0:
+        print(json.dumps({"suite": rows, "n_gpus": world, "status": status, "peaks": peaks,
+                          "timing": "median of %d launches, 512 MB L2 flush before each, CUDA events, max over ranks" % iters}))
+    if world > 1:
+        dist.destroy_process_group()
+
 def run_profile_case(args):
     """Small single-GPU cases for profiler captures (a few hundred MB, three launches): the
     numbers printed here are not benchmark values."""
@@ -410,11 +552,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--suite", action="store_true",
+                    help="time all five configurations at the current world size and print one JSON object")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="run a small case three times for a profiler capture and exit")
     args = ap.parse_args()
     if args.profile:
         run_profile_case(args)
+        return
+    if args.suite:
+        run_suite(args)
         return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
