@@ -38,7 +38,7 @@ reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
                          int64_t num_slots, int64_t key_stride, int64_t value_stride,
                          unsigned int *status) {
   __shared__ int64_t s_slot[kTok];
-  __shared__ __align__(16) __nv_bfloat16 s_v[kD][kTok + 8];  // [d][tok], padded row = 48 B
+  __shared__ __align__(16) __nv_bfloat16 s_v[kTok][kD + 8];  // [tok][d], rows of 272 B
   const int t0 = blockIdx.x * kTok;
   const int h = blockIdx.y;
   const int tid = threadIdx.x;
@@ -69,36 +69,36 @@ reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
       *reinterpret_cast<uint4 *>(dst) = val;
     }
   }
-  // ---- V: stage transposed --------------------------------------------------------------
+  // ---- V: stage token-major (16-byte shared stores, conflict-free), read it back by column ---
   {
     const int tok = tid >> 4, part = tid & 15;
-    if (s_slot[tok] >= 0) {
-      const uint4 val = *reinterpret_cast<const uint4 *>(
+    if (s_slot[tok] >= 0)
+      *reinterpret_cast<uint4 *>(&s_v[tok][part * kX]) = *reinterpret_cast<const uint4 *>(
           value + (int64_t)(t0 + tok) * value_stride + h * kD + part * kX);
-      const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&val);
-#pragma unroll
-      for (int j = 0; j < kX; ++j) s_v[part * kX + j][tok] = e[j];
-    }
   }
   __syncthreads();
   {
-    const int d = tid >> 1, half = tid & 1;
+    // a warp covers 32 consecutive d of one token half: column reads hit 16 distinct banks
+    const int d = tid & (kD - 1), half = tid >> 7;
     const int tb = half * 8;
     const int64_t s0 = s_slot[tb];
     bool run = s0 >= 0 && (s0 % 8) == 0;
 #pragma unroll
     for (int j = 1; j < 8; ++j) run = run && (s_slot[tb + j] == s0 + j);
     if (run) {
+      uint4 val;
+      __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&val);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = s_v[tb + j][d];
       const int64_t blk = s0 / kB, off = s0 % kB;
-      __nv_bfloat16 *dst = value_cache + ((blk * num_kv_heads + h) * kD + d) * kB + off;
-      *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(&s_v[d][tb]);
+      *reinterpret_cast<uint4 *>(value_cache + ((blk * num_kv_heads + h) * kD + d) * kB + off) = val;
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int64_t slot = s_slot[tb + j];
         if (slot >= 0) {
           const int64_t blk = slot / kB, off = slot % kB;
-          value_cache[((blk * num_kv_heads + h) * kD + d) * kB + off] = s_v[d][tb + j];
+          value_cache[((blk * num_kv_heads + h) * kD + d) * kB + off] = s_v[tb + j][d];
         }
       }
     }
@@ -114,7 +114,7 @@ gather_cached_kv_kernel(__nv_bfloat16 *__restrict__ key, __nv_bfloat16 *__restri
                         int num_kv_heads, int64_t num_slots, int64_t key_stride,
                         int64_t value_stride, unsigned int *status) {
   __shared__ int64_t s_slot[kTok];
-  __shared__ __align__(16) __nv_bfloat16 s_v[kD][kTok + 8];
+  __shared__ __align__(16) __nv_bfloat16 s_v[kTok][kD + 8];  // [tok][d], rows of 272 B
   const int t0 = blockIdx.x * kTok;
   const int h = blockIdx.y;
   const int tid = threadIdx.x;
@@ -143,7 +143,7 @@ gather_cached_kv_kernel(__nv_bfloat16 *__restrict__ key, __nv_bfloat16 *__restri
     }
   }
   {
-    const int d = tid >> 1, half = tid & 1;
+    const int d = tid & (kD - 1), half = tid >> 7;
     const int tb = half * 8;
     const int64_t s0 = s_slot[tb];
     bool run = s0 >= 0 && (s0 % 8) == 0;
@@ -151,15 +151,18 @@ gather_cached_kv_kernel(__nv_bfloat16 *__restrict__ key, __nv_bfloat16 *__restri
     for (int j = 1; j < 8; ++j) run = run && (s_slot[tb + j] == s0 + j);
     if (run) {
       const int64_t blk = s0 / kB, off = s0 % kB;
-      *reinterpret_cast<uint4 *>(&s_v[d][tb]) = *reinterpret_cast<const uint4 *>(
+      const uint4 val = *reinterpret_cast<const uint4 *>(
           value_cache + ((blk * num_kv_heads + h) * kD + d) * kB + off);
+      const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&val);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s_v[tb + j][d] = e[j];
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int64_t slot = s_slot[tb + j];
         if (slot >= 0) {
           const int64_t blk = slot / kB, off = slot % kB;
-          s_v[d][tb + j] = value_cache[((blk * num_kv_heads + h) * kD + d) * kB + off];
+          s_v[tb + j][d] = value_cache[((blk * num_kv_heads + h) * kD + d) * kB + off];
         }
       }
     }
@@ -167,14 +170,9 @@ gather_cached_kv_kernel(__nv_bfloat16 *__restrict__ key, __nv_bfloat16 *__restri
   __syncthreads();
   {
     const int tok = tid >> 4, part = tid & 15;
-    if (s_slot[tok] >= 0) {
-      uint4 val;
-      __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&val);
-#pragma unroll
-      for (int j = 0; j < kX; ++j) e[j] = s_v[part * kX + j][tok];
-      *reinterpret_cast<uint4 *>(value + (int64_t)(t0 + tok) * value_stride + h * kD +
-                                 part * kX) = val;
-    }
+    if (s_slot[tok] >= 0)
+      *reinterpret_cast<uint4 *>(value + (int64_t)(t0 + tok) * value_stride + h * kD + part * kX) =
+          *reinterpret_cast<const uint4 *>(&s_v[tok][part * kX]);
   }
 }
 
@@ -221,16 +219,17 @@ copy_blocks_kernel(const int64_t *__restrict__ key_cache_ptrs,
                  static_cast<int>(bytes_per_block / 16));
 }
 
-// Same copy with the tables passed by value in the kernel-argument buffer (< 4 KB).
+// Same copy with the tables passed by value in the kernel-argument buffer (sm_70+ accepts
+// up to 32764 bytes of arguments; this struct is 26112 bytes).
 constexpr int kArgLayers = 96;
-constexpr int kArgPairs = 192;
+constexpr int kArgPairs = 3072;
 struct CopyArgs {
   int64_t key_ptrs[kArgLayers];
   int64_t value_ptrs[kArgLayers];
   int32_t src[kArgPairs];
   int32_t dst[kArgPairs];
 };
-static_assert(sizeof(CopyArgs) <= 3072 + 64, "kernel arguments must stay below 4 KB");
+static_assert(sizeof(CopyArgs) + 64 <= 32764, "kernel arguments must stay below the 32764-byte limit");
 
 __global__ void __launch_bounds__(kCopyThreads)
 copy_blocks_args_kernel(const __grid_constant__ CopyArgs args, int num_layers,
@@ -383,8 +382,7 @@ extern "C" char *aici_copy_blocks_host(const int64_t *key_cache_ptrs_host,
     const int nl = num_layers - l0 < kArgLayers ? num_layers - l0 : kArgLayers;
     for (int p0 = 0; p0 < num_pairs; p0 += kArgPairs) {
       const int np = num_pairs - p0 < kArgPairs ? num_pairs - p0 : kArgPairs;
-      CopyArgs args;
-      memset(&args, 0, sizeof(args));
+      static thread_local CopyArgs args;
       for (int l = 0; l < nl; ++l) {
         args.key_ptrs[l] = key_cache_ptrs_host[l0 + l];
         args.value_ptrs[l] = value_cache_ptrs_host[l0 + l];

@@ -170,9 +170,10 @@ def gather_cached_kv(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Te
 
 
 def copy_blocks(key_caches: Sequence[torch.Tensor], value_caches: Sequence[torch.Tensor],
-                block_mapping: Dict[int, List[int]]) -> None:
-    """For every layer and every src -> dst in block_mapping copy one key block and one value
-    block (lib.rs:276-331).  The layer addresses and the pairs go to the kernel as arguments
+                block_mapping) -> None:
+    """For every layer and every src -> dst in block_mapping (a dict src -> [dst, ...] as in the
+    crate, or the same pairs already flattened into an int64 CPU tensor) copy one key block and
+    one value block (lib.rs:276-331).  The layer addresses and the pairs go to the kernel as arguments
     from host memory, so nothing is uploaded and nothing synchronises."""
     fn = "copy_blocks"
     num_layers = len(key_caches)
@@ -191,16 +192,23 @@ def copy_blocks(key_caches: Sequence[torch.Tensor], value_caches: Sequence[torch
             raise AiciError("%s: caches must be contiguous bf16 or f16" % fn)
     num_blocks, num_heads, head_size, block_size = value_caches[0].shape
     numel_per_block = num_heads * head_size * block_size
-    pairs: List[int] = []
-    for src, dsts in block_mapping.items():
-        for dst in dsts:
-            pairs += [int(src), int(dst)]
-    num_pairs = len(pairs) // 2
+    if isinstance(block_mapping, torch.Tensor):
+        # already flattened (src, dst, src, dst, ...) int64 host tensor: no per-pair Python work
+        if block_mapping.dtype != torch.int64 or block_mapping.is_cuda or not block_mapping.is_contiguous():
+            raise AiciError("%s: a flattened block_mapping must be a contiguous int64 CPU tensor" % fn)
+        flat = block_mapping
+    else:
+        pairs: List[int] = []
+        for src, dsts in block_mapping.items():
+            for dst in dsts:
+                pairs += [int(src), int(dst)]
+        flat = torch.tensor(pairs, dtype=torch.int64)
+    num_pairs = flat.numel() // 2
     if num_pairs == 0:
         return
     kp = (ctypes.c_int64 * num_layers)(*[t.data_ptr() for t in key_caches])
     vp = (ctypes.c_int64 * num_layers)(*[t.data_ptr() for t in value_caches])
-    mp = (ctypes.c_int64 * len(pairs))(*pairs)
+    mp = ctypes.c_void_p(flat.data_ptr())
     with torch.cuda.device(dev):
         res = _lib.lib().aici_copy_blocks_host(
             kp, vp, mp, ctypes.c_int(num_layers), ctypes.c_int(num_pairs),

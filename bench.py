@@ -481,7 +481,8 @@ def run_suite(args):
             rows_ = [w.block_tables[i, :(c + 15) // 16].tolist() for i, c in enumerate(w.context_list)]
             mapping = workloads.fork_block_mapping(rows_, 8, 4, free, whole_sequence=True)
             pairs = sum(len(v) for v in mapping.values())
-            c_ms, _ = timed(lambda: tch_cuda.copy_blocks([w.key_cache], [w.value_cache], mapping))
+            flat = torch.tensor([x for s_, ds in mapping.items() for d_ in ds for x in (s_, d_)], dtype=torch.int64)
+            c_ms, _ = timed(lambda: tch_cuda.copy_blocks([w.key_cache], [w.value_cache], flat))
             blk_bytes = w.num_kv_heads * 128 * 16 * 2
             add("5-copy_blocks whole-sequence fork (%d pairs, 1 layer)" % pairs, "hbm",
                 pairs * 2 * blk_bytes * 2, c_ms, 0.0)
