@@ -28,7 +28,8 @@ constexpr int kPanelBytes = 128 * 128; // [128 rows][64 bf16] = one 128B-swizzle
 constexpr int kTileBytes = 2 * kPanelBytes;
 constexpr int kPrefillThreads = 192;
 constexpr uint32_t kTmemCols = 256;    // S/P: columns [0,128), O: columns [128,256)
-constexpr float kRescaleThreshold = 8.f;  // log2 units; P stays below 2^8 between rescales
+constexpr float kRescaleThreshold = 8.f;  // log2 units: the running reference moves once a score exceeds it by this
+constexpr float kDangerThreshold = 60.f;  // beyond this a tile is redone against its exact maximum (no overflow risk)
 
 struct PrefillParams {
   __nv_bfloat16 *out;
@@ -176,8 +177,8 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t t_s = tmem_base + ((uint32_t)(warp * 32) << 16);
     const uint32_t t_o = t_s + 128;
     const float sc = p.scale_log2e;
-    float m_used = -INFINITY, l_sum = 0.f;
-    bool ok = true;
+    float m_used = -INFINITY, m_next = -INFINITY, l_sum = 0.f;
+    bool ok = true, pending = false;
 
     for (int j = 0; j < n_tiles; ++j) {
       ok = mbar_wait_abortable(&sh->s_full, (uint32_t)j & 1u, p.status);
@@ -185,76 +186,154 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (!ok) break;
       tc_fence_after();
       const int n0 = j * kBN;
-      uint32_t r[32];
+      // A rescale that the previous tile found necessary but left for now: the previous P V has
+      // completed (s_full of this tile is committed after it), so O can be touched.
+      if (__any_sync(0xffffffffu, pending)) {
+        float alpha = 1.f;
+        if (pending) {
+          alpha = fast_exp2(m_used - m_next);
+          m_used = m_next;
+          l_sum *= alpha;
+          pending = false;
+        }
+        uint32_t o[32];
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          tmem_ld32(t_o + 32 * c4, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(t_o + 32 * c4, o);
+        }
+        tmem_wait_st();
+      }
 
-      // pass 1: row max of the raw scores over visible columns
-      float mx = -INFINITY;
+      const bool full_tile = n0 + kBN <= lim_row;
+      bool exact_path = (j == 0) || __any_sync(0xffffffffu, m_used == -INFINITY);
+      if (!exact_path) {
+        // ---- single pass against the running reference m_used --------------------------------
+        // P is computed for the whole row in registers while S is still intact; if some score
+        // exceeds the reference by more than kDangerThreshold the tile is redone exactly, if by
+        // more than kRescaleThreshold the reference moves after this tile's P V (pending).
+        uint32_t pk[64];
+        uint32_t ra[32], rb[32];
+        float xmax = -INFINITY, l0 = 0.f, l1 = 0.f;
+        tmem_ld32(t_s, ra);
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        tmem_ld32(t_s + 32 * c4, r);
-        tmem_wait_ld();
-        const int cb = n0 + 32 * c4;
-        if (cb + 32 <= lim_row) {
+        for (int c4 = 0; c4 < 4; ++c4) {
+          tmem_wait_ld();
+          uint32_t(&cur)[32] = (c4 & 1) ? rb : ra;
+          uint32_t(&nxt)[32] = (c4 & 1) ? ra : rb;
+          if (c4 < 3) tmem_ld32(t_s + 32 * (c4 + 1), nxt);
+          if (full_tile) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+            for (int i = 0; i < 32; i += 2) {
+              const float x0 = fmaf(__uint_as_float(cur[i]), sc, -m_used);
+              const float x1 = fmaf(__uint_as_float(cur[i + 1]), sc, -m_used);
+              xmax = fmaxf(xmax, fmaxf(x0, x1));
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              l0 += p0;
+              l1 += p1;
+              pk[16 * c4 + (i >> 1)] = pack_bf16(p0, p1);
+            }
+          } else {
+            const int cb = n0 + 32 * c4;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float x0 = (cb + i < lim_row) ? fmaf(__uint_as_float(cur[i]), sc, -m_used) : -INFINITY;
+              const float x1 = (cb + i + 1 < lim_row) ? fmaf(__uint_as_float(cur[i + 1]), sc, -m_used) : -INFINITY;
+              xmax = fmaxf(xmax, fmaxf(x0, x1));
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              l0 += p0;
+              l1 += p1;
+              pk[16 * c4 + (i >> 1)] = pack_bf16(p0, p1);
+            }
+          }
+        }
+        if (__any_sync(0xffffffffu, xmax > kDangerThreshold)) {
+          exact_path = true;  // S is untouched: redo the tile with an exact maximum
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (cb + i < lim_row) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int c4 = 0; c4 < 4; ++c4)
+            tmem_st16(t_s + 16 * c4, *reinterpret_cast<uint32_t(*)[16]>(&pk[16 * c4]));
+          l_sum += l0 + l1;
+          if (xmax > kRescaleThreshold) {
+            pending = true;
+            m_next = m_used + xmax;
+          }
         }
       }
-      mx *= sc;  // scale > 0, so the order is preserved
-
-      // lazy rescale of the running output
-      if (j == 0) {
-        m_used = mx;
-      } else {
-        const bool need = mx > m_used + kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {
-          float alpha = 1.f;
-          if (need) {
-            alpha = fast_exp2(m_used - mx);  // 0 when nothing was visible so far
-            m_used = mx;
-            l_sum *= alpha;
-          }
+      if (exact_path) {
+        uint32_t r[32];
+        // pass 1: row max of the raw scores over visible columns
+        float mx = -INFINITY;
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            tmem_ld32(t_o + 32 * c4, r);
-            tmem_wait_ld();
+        for (int c4 = 0; c4 < 4; ++c4) {
+          tmem_ld32(t_s + 32 * c4, r);
+          tmem_wait_ld();
+          const int cb = n0 + 32 * c4;
+          if (cb + 32 <= lim_row) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(t_o + 32 * c4, r);
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (cb + i < lim_row) mx = fmaxf(mx, __uint_as_float(r[i]));
           }
-          tmem_wait_st();
         }
-      }
-      const float base = (m_used == -INFINITY) ? 0.f : m_used;
+        mx *= sc;  // scale > 0, so the order is preserved
 
-      // pass 2: p = exp2(s * scale - base), row sum, bf16 P over the S columns
-#pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        tmem_ld32(t_s + 32 * c4, r);
-        tmem_wait_ld();
-        const int cb = n0 + 32 * c4;
-        uint32_t pk[16];
-        if (cb + 32 <= lim_row) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), sc, -base));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), sc, -base));
-            l_sum += p0 + p1;
-            pk[i >> 1] = pack_bf16(p0, p1);
-          }
+        // immediate rescale of the running output
+        if (j == 0) {
+          m_used = mx;
         } else {
+          const bool need = mx > m_used + kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            float alpha = 1.f;
+            if (need) {
+              alpha = fast_exp2(m_used - mx);  // 0 when nothing was visible so far
+              m_used = mx;
+              l_sum *= alpha;
+            }
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = (cb + i < lim_row) ? fast_exp2(fmaf(__uint_as_float(r[i]), sc, -base)) : 0.f;
-            const float p1 = (cb + i + 1 < lim_row) ? fast_exp2(fmaf(__uint_as_float(r[i + 1]), sc, -base)) : 0.f;
-            l_sum += p0 + p1;
-            pk[i >> 1] = pack_bf16(p0, p1);
+            for (int c4 = 0; c4 < 4; ++c4) {
+              tmem_ld32(t_o + 32 * c4, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st32(t_o + 32 * c4, r);
+            }
+            tmem_wait_st();
           }
         }
-        tmem_st16(t_s + 16 * c4, pk);
+        const float base = (m_used == -INFINITY) ? 0.f : m_used;
+
+        // pass 2: p = exp2(s * scale - base), row sum, bf16 P over the S columns
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          tmem_ld32(t_s + 32 * c4, r);
+          tmem_wait_ld();
+          const int cb = n0 + 32 * c4;
+          uint32_t pk[16];
+          if (cb + 32 <= lim_row) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), sc, -base));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), sc, -base));
+              l_sum += p0 + p1;
+              pk[i >> 1] = pack_bf16(p0, p1);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = (cb + i < lim_row) ? fast_exp2(fmaf(__uint_as_float(r[i]), sc, -base)) : 0.f;
+              const float p1 = (cb + i + 1 < lim_row) ? fast_exp2(fmaf(__uint_as_float(r[i + 1]), sc, -base)) : 0.f;
+              l_sum += p0 + p1;
+              pk[i >> 1] = pack_bf16(p0, p1);
+            }
+          }
+          tmem_st16(t_s + 16 * c4, pk);
+        }
       }
       tmem_wait_st();
       tc_fence_before();

@@ -412,10 +412,10 @@ def run_suite(args):
         """median device time of fn over `iters` launches, L2 flushed before each; max over ranks"""
         ks, gs = [], []
         for i in range(warm + iters):
-            flush.zero_()
-            a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
             if world > 1:
                 dist.barrier()
+            flush.zero_()  # also gives the host time to queue the launches behind it
+            a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
             a.record()
             o = fn()
             b.record()

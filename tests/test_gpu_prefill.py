@@ -86,6 +86,25 @@ def test_large_scores_exercise_the_lazy_rescale(cuda_device):
     assert mx <= 4e-2 and mean <= MEAN_ABS, (mx, mean)  # peaked softmax: |out| up to ~4, bf16 ulp 1.6e-2
 
 
+def test_score_jump_beyond_the_single_pass_range(cuda_device):
+    """Keys of the last tiles are 8x larger: scores jump by far more than the range the single-pass
+    softmax may absorb, so those tiles must be redone against their exact maximum (no inf/NaN)."""
+    n, hq = 640, 2
+    g = torch.Generator(device=cuda_device).manual_seed(82)
+    q = workloads.randn_bf16((n, hq, 128), cuda_device, g)
+    k = workloads.randn_bf16((n, hq, 128), cuda_device, g)
+    v = workloads.randn_bf16((n, hq, 128), cuda_device, g)
+    k[384:] = (k[384:].float() * 8).to(torch.bfloat16)
+    k[600:] = (k[600:].float() * 4).to(torch.bfloat16)
+    cu = torch.tensor([0, n], dtype=torch.int32, device=cuda_device)
+    out = tch_cuda.flash_attn_varlen(q, k, v, cu, cu, n, n, 1.0, True)
+    want = O.flash_attn_varlen(q.cpu(), k.cpu(), v.cpu(), cu.cpu(), cu.cpu(), n, n, 1.0, True)
+    got = out.cpu().float()
+    assert torch.isfinite(got).all()
+    mx, mean = O.error_stats(got, want)
+    assert mx <= 4e-2 and mean <= MEAN_ABS, (mx, mean)  # one-hot softmax rows: |out| up to ~4
+
+
 def test_mixed_step_prefill_chunks(cuda_device):
     w = workloads.prefill_mixed_chunks(cuda_device)
     _check_full(w, _run(cuda_device, w))
