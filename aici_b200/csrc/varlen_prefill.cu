@@ -7,27 +7,33 @@
 // head / (num_heads / num_heads_k), causal mask aligned to the bottom-right corner
 // (softmax.h:159-168), rows that see no column give 0 (flash_fwd_kernel.h:1056).
 //
-// One CTA owns one 128-row query tile of one (sequence, head) and walks its key/value tiles of
-// 128 tokens.  Two CTAs share an SM (96 KB of shared memory and 256 TMEM columns each), so one
-// CTA's softmax overlaps the other's tensor-core work.
-//   warp 4   : TMA producer (Q once, then K_j and V_j into single buffers, 128B-swizzled)
-//   warp 5   : TMEM owner and MMA issuer: S = Q K_j^T (SS form), then O += P_j V_j with P read
-//              from TMEM (TS form) and V as an MN-major shared-memory operand
-//   warps 0-3: one query row per thread (= one TMEM lane): read S with tcgen05.ld, mask, running
-//              max with lazy rescale of O, exp2, row sum, bf16 P written back over S with
-//              tcgen05.st; at the end O / sum -> bf16 -> swizzled staging -> coalesced stores
+// One CTA per SM owns TWO 128-row query tiles that share their key/value tiles: two query heads
+// of one kv-head group when the group size is even (same rows, same causal extent), else two
+// consecutive row tiles of one head.  Each key/value tile of 128 tokens is loaded once for both.
+//   warp 8    : TMA producer (Q0, Q1 once; then K_0, V_0, K_1, V_1, ... through a 4-stage ring of
+//               32 KB stages, 128-byte swizzle, no multicast)
+//   warp 9    : TMEM owner (all 512 columns: S0, S1, O0, O1) and MMA issuer.  S_t = Q_t K_j^T in SS
+//               form, O_t += P_t V_j in TS form (P read from TMEM where it overwrote S_t, V as an
+//               MN-major shared-memory operand).  Issue order S0 S1 | PV0 S0' PV1 S1' | ... so that
+//               the tensor pipe works on one tile while the other tile's softmax runs.
+//   warps 0-3 : softmax of tile 0, warps 4-7: softmax of tile 1.  One query row per thread (= one
+//               TMEM lane): tcgen05.ld the scores, mask, exp2 against a running reference maximum
+//               (single pass; the reference moves lazily and a tile whose scores jump too far is
+//               redone exactly), row sum, bf16 P written back with tcgen05.st; at the end
+//               O / sum -> bf16 -> swizzled staging in the tile's Q buffer -> coalesced stores.
 // Every barrier wait is bounded; a timeout sets AICI_STATUS_WAIT_TIMEOUT and unwinds.
 #include "tcgen05.cuh"
 
 namespace aici {
 
-constexpr int kBM = 128;               // query rows per CTA
+constexpr int kBM = 128;               // query rows per tile
 constexpr int kBN = 128;               // keys per tile
 constexpr int kHD = 128;               // head size
 constexpr int kPanelBytes = 128 * 128; // [128 rows][64 bf16] = one 128B-swizzled panel
 constexpr int kTileBytes = 2 * kPanelBytes;
-constexpr int kPrefillThreads = 192;
-constexpr uint32_t kTmemCols = 256;    // S/P: columns [0,128), O: columns [128,256)
+constexpr int kKvStages = 4;           // ring of K/V tiles (K_j and V_j alternate)
+constexpr int kPrefillThreads = 320;   // 8 softmax warps + producer + MMA issuer
+constexpr uint32_t kTmemCols = 512;    // S0/P0 [0,128) S1/P1 [128,256) O0 [256,384) O1 [384,512)
 constexpr float kRescaleThreshold = 8.f;  // log2 units: the running reference moves once a score exceeds it by this
 constexpr float kDangerThreshold = 60.f;  // beyond this a tile is redone against its exact maximum (no overflow risk)
 
@@ -38,64 +44,108 @@ struct PrefillParams {
   int64_t o_tok_stride, o_head_stride;
   int group;
   int causal;
+  int pair_heads;  // 1: the two tiles are heads 2y and 2y+1; 0: two consecutive row tiles of head y
   float scale_log2e;
   unsigned int *status;
 };
 
 struct PrefillSmem {
-  uint64_t q_full, k_full, v_full, k_empty, v_empty, s_full, p_ready, o_full, staged;
+  uint64_t q_full[2], kv_full[kKvStages], kv_empty[kKvStages], s_full[2], p_ready[2], o_full[2], staged[2], drain;
   uint32_t tmem_base;
   uint32_t aborted;
 };
 
-constexpr int kPrefillSmemBytes = 3 * kTileBytes + 1024 /*align*/ + 256 /*PrefillSmem*/;
+struct TileInfo {
+  int h;        // query head
+  int m0;       // first query row within the sequence
+  int rows;     // valid rows (<= 128); 0 = this tile does not exist
+  int n_tiles;  // key/value tiles it visits; 0 = nothing visible
+};
 
-__global__ void __launch_bounds__(kPrefillThreads, 2)
+constexpr int kPrefillSmemBytes = (2 + kKvStages) * kTileBytes + 1024 /*align*/ + 256 /*PrefillSmem*/;
+
+__device__ __forceinline__ void zero_rows(const PrefillParams &p, int q0, const TileInfo &T, int tid,
+                                          int nthreads) {
+  for (int i = tid; i < T.rows * (kHD / 8); i += nthreads) {
+    const int r = i / (kHD / 8), c = i % (kHD / 8);
+    *reinterpret_cast<uint4 *>(p.out + (int64_t)(q0 + T.m0 + r) * p.o_tok_stride +
+                               (int64_t)T.h * p.o_head_stride + c * 8) = make_uint4(0, 0, 0, 0);
+  }
+}
+
+__global__ void __launch_bounds__(kPrefillThreads, 1)
 varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int b = blockIdx.z, h = blockIdx.y, hk = h / p.group;
+  const int b = blockIdx.z;
   const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
   const int k0 = p.cu_k[b], lk = p.cu_k[b + 1] - k0;
   const int n_mblocks = (lq + kBM - 1) / kBM;
-  if ((int)blockIdx.x >= n_mblocks) return;
-  const int m0 = (n_mblocks - 1 - (int)blockIdx.x) * kBM;  // longest causal tiles first
-  const int rows = min(kBM, lq - m0);
 
-  int lim_tile = lk;
-  if (p.causal) lim_tile = min(lk, m0 + rows + lk - lq);
-  const int n_tiles = lim_tile > 0 ? (lim_tile + kBN - 1) / kBN : 0;
-
-  if (n_tiles == 0 || (*reinterpret_cast<volatile unsigned int *>(p.status) & AICI_STATUS_WAIT_TIMEOUT)) {
-    // nothing visible (or the device already reported a stuck pipeline): rows are zero
-    for (int i = tid; i < rows * (kHD / 8); i += kPrefillThreads) {
-      const int r = i / (kHD / 8), c = i % (kHD / 8);
-      *reinterpret_cast<uint4 *>(p.out + (int64_t)(q0 + m0 + r) * p.o_tok_stride +
-                                 (int64_t)h * p.o_head_stride + c * 8) = make_uint4(0, 0, 0, 0);
+  // ---- which two tiles does this CTA own? (longest causal tiles are scheduled first) ----------
+  TileInfo tiles[2];
+  {
+    int mb[2], hh[2];
+    if (p.pair_heads) {
+      mb[0] = mb[1] = n_mblocks - 1 - (int)blockIdx.x;
+      hh[0] = 2 * (int)blockIdx.y;
+      hh[1] = hh[0] + 1;
+    } else {
+      mb[1] = n_mblocks - 1 - 2 * (int)blockIdx.x;
+      mb[0] = mb[1] - 1;
+      hh[0] = hh[1] = (int)blockIdx.y;
     }
-    return;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      TileInfo &T = tiles[t];
+      T.h = hh[t];
+      T.m0 = mb[t] * kBM;
+      T.rows = mb[t] >= 0 && mb[t] < n_mblocks ? min(kBM, lq - T.m0) : 0;
+      int lim = lk;
+      if (p.causal) lim = min(lk, T.m0 + T.rows + lk - lq);
+      T.n_tiles = (T.rows > 0 && lim > 0) ? (lim + kBN - 1) / kBN : 0;
+    }
   }
+  if (tiles[0].rows == 0 && tiles[1].rows == 0) return;
+  const int hk = tiles[1].rows > 0 ? tiles[1].h / p.group : tiles[0].h / p.group;
+  const bool stuck = (*reinterpret_cast<volatile unsigned int *>(p.status) & AICI_STATUS_WAIT_TIMEOUT) != 0;
+  if (stuck) {  // the device already reported a stuck pipeline: do not start another one
+    tiles[0].n_tiles = 0;
+    tiles[1].n_tiles = 0;
+  }
+  // tiles that see no key at all are zero rows (flash_fwd_kernel.h:1056)
+  if (tiles[0].rows > 0 && tiles[0].n_tiles == 0) zero_rows(p, q0, tiles[0], tid, kPrefillThreads);
+  if (tiles[1].rows > 0 && tiles[1].n_tiles == 0) zero_rows(p, q0, tiles[1], tid, kPrefillThreads);
+  const int nt0 = tiles[0].n_tiles, nt1 = tiles[1].n_tiles;
+  const int nmax = max(nt0, nt1);
+  if (nmax == 0) return;
 
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t *sQ = smem, *sK = smem + kTileBytes, *sV = smem + 2 * kTileBytes;
-  PrefillSmem *sh = reinterpret_cast<PrefillSmem *>(smem + 3 * kTileBytes);
+  uint8_t *sQ = smem;                       // two tiles
+  uint8_t *sKV = smem + 2 * kTileBytes;     // kKvStages tiles
+  PrefillSmem *sh = reinterpret_cast<PrefillSmem *>(smem + (2 + kKvStages) * kTileBytes);
 
   if (tid == 0) {
-    mbar_init(&sh->q_full, 1);
-    mbar_init(&sh->k_full, 1);
-    mbar_init(&sh->v_full, 1);
-    mbar_init(&sh->k_empty, 1);
-    mbar_init(&sh->v_empty, 1);
-    mbar_init(&sh->s_full, 1);
-    mbar_init(&sh->p_ready, 4);
-    mbar_init(&sh->o_full, 1);
-    mbar_init(&sh->staged, 4);
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&sh->q_full[t], 1);
+      mbar_init(&sh->s_full[t], 1);
+      mbar_init(&sh->p_ready[t], 4);
+      mbar_init(&sh->o_full[t], 1);
+      mbar_init(&sh->staged[t], 4);
+    }
+#pragma unroll
+    for (int s = 0; s < kKvStages; ++s) {
+      mbar_init(&sh->kv_full[s], 1);
+      mbar_init(&sh->kv_empty[s], 1);
+    }
+    mbar_init(&sh->drain, 1);
     sh->aborted = 0;
     fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&sh->tmem_base, kTmemCols);
     tmem_relinquish();
   }
@@ -104,84 +154,124 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------------------------------------------------------- TMA producer -----------
     if (lane == 0) {
       tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
-      mbar_expect_tx(&sh->q_full, kTileBytes);
-      tma_load_3d(sQ, &tmap_q, 0, h, q0 + m0, &sh->q_full);
-      tma_load_3d(sQ + kPanelBytes, &tmap_q, 64, h, q0 + m0, &sh->q_full);
-      for (int j = 0; j < n_tiles; ++j) {
-        const uint32_t ph = (uint32_t)j & 1u;
-        if (!mbar_wait_abortable(&sh->k_empty, ph ^ 1u, p.status)) break;
-        mbar_expect_tx(&sh->k_full, kTileBytes);
-        tma_load_3d(sK, &tmap_k, 0, hk, k0 + j * kBN, &sh->k_full);
-        tma_load_3d(sK + kPanelBytes, &tmap_k, 64, hk, k0 + j * kBN, &sh->k_full);
-        if (!mbar_wait_abortable(&sh->v_empty, ph ^ 1u, p.status)) break;
-        mbar_expect_tx(&sh->v_full, kTileBytes);
-        tma_load_3d(sV, &tmap_v, 0, hk, k0 + j * kBN, &sh->v_full);
-        tma_load_3d(sV + kPanelBytes, &tmap_v, 64, hk, k0 + j * kBN, &sh->v_full);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (tiles[t].n_tiles > 0) {
+          mbar_expect_tx(&sh->q_full[t], kTileBytes);
+          tma_load_3d(sQ + t * kTileBytes, &tmap_q, 0, tiles[t].h, q0 + tiles[t].m0, &sh->q_full[t]);
+          tma_load_3d(sQ + t * kTileBytes + kPanelBytes, &tmap_q, 64, tiles[t].h, q0 + tiles[t].m0,
+                      &sh->q_full[t]);
+        }
+      }
+      for (int i = 0; i < 2 * nmax; ++i) {  // i even: K_{i/2}, i odd: V_{i/2}
+        const int stage = i % kKvStages;
+        if (!mbar_wait_abortable(&sh->kv_empty[stage], (((uint32_t)i / kKvStages) & 1u) ^ 1u, p.status)) break;
+        uint8_t *dst = sKV + stage * kTileBytes;
+        const CUtensorMap *tm = (i & 1) ? &tmap_v : &tmap_k;
+        mbar_expect_tx(&sh->kv_full[stage], kTileBytes);
+        tma_load_3d(dst, tm, 0, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
+        tma_load_3d(dst + kPanelBytes, tm, 64, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer -------------
     constexpr uint32_t idesc_s = idesc_bf16(kBM, kBN, false);
     constexpr uint32_t idesc_pv = idesc_bf16(kBM, kHD, true);
-    // Q, K: K-major, rows of 128 B, 8-row groups 1024 B apart; two 64-column panels.
-    const uint64_t qdesc = smem_desc_sw128(smem_u32(sQ), 16, 1024);
-    const uint64_t kdesc = smem_desc_sw128(smem_u32(sK), 16, 1024);
-    // V as B operand of P V: N (= d) contiguous, 64 d per swizzle atom, second atom one panel
-    // further (leading offset), 8-token groups 1024 B apart (stride offset).
-    const uint64_t vdesc = smem_desc_sw128(smem_u32(sV), kPanelBytes, 1024);
-    bool ok = __all_sync(0xffffffffu, mbar_wait_abortable(&sh->q_full, 0, p.status));
-    for (int j = 0; ok && j < n_tiles; ++j) {
-      const uint32_t ph = (uint32_t)j & 1u;
-      ok = __all_sync(0xffffffffu, mbar_wait_abortable(&sh->k_full, ph, p.status));
-      if (!ok) break;
+    bool ok = true;
+    auto wait = [&](uint64_t *bar, uint32_t parity) {
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait_abortable(bar, parity, p.status));
+      return ok;
+    };
+    auto wait_kv = [&](int i) { return wait(&sh->kv_full[i % kKvStages], ((uint32_t)i / kKvStages) & 1u); };
+    // S_t = Q_t K^T.  Q, K: K-major, rows of 128 B, 8-row groups 1024 B apart, two 64-column panels.
+    auto issue_s = [&](int t, int i_k) {
       tc_fence_after();
       if (lane == 0) {
+        const uint64_t qdesc = smem_desc_sw128(smem_u32(sQ + t * kTileBytes), 16, 1024);
+        const uint64_t kdesc = smem_desc_sw128(smem_u32(sKV + (i_k % kKvStages) * kTileBytes), 16, 1024);
 #pragma unroll
         for (int ks = 0; ks < kHD / 16; ++ks) {
           const uint64_t adv = (uint64_t)(((ks >> 2) * kPanelBytes + (ks & 3) * 32) >> 4);
-          umma_ss(tmem_base, qdesc + adv, kdesc + adv, idesc_s, ks > 0 ? 1u : 0u);
+          umma_ss(tmem_base + t * 128, qdesc + adv, kdesc + adv, idesc_s, ks > 0 ? 1u : 0u);
         }
-        tc_commit(&sh->k_empty);
-        tc_commit(&sh->s_full);
+        tc_commit(&sh->s_full[t]);
       }
       __syncwarp();
-      ok = mbar_wait_abortable(&sh->p_ready, ph, p.status) &&
-           mbar_wait_abortable(&sh->v_full, ph, p.status);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+    };
+    // O_t += P_t V.  V as B operand: N (= d) contiguous, 64 d per swizzle atom, second atom one
+    // panel further (leading offset), 8-token groups 1024 B apart (stride offset).
+    auto issue_pv = [&](int t, int i_v, bool first, bool last) {
       tc_fence_after();
       if (lane == 0) {
+        const uint64_t vdesc = smem_desc_sw128(smem_u32(sKV + (i_v % kKvStages) * kTileBytes), kPanelBytes, 1024);
 #pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks) {
-          umma_ts(tmem_base + 128, tmem_base + 8 * ks, vdesc + (uint64_t)((ks * 2048) >> 4),
-                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        }
-        tc_commit(&sh->v_empty);
-        if (j == n_tiles - 1) tc_commit(&sh->o_full);
+        for (int ks = 0; ks < kBN / 16; ++ks)
+          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + 8 * ks, vdesc + (uint64_t)((ks * 2048) >> 4),
+                  idesc_pv, (!first || ks > 0) ? 1u : 0u);
+        if (last) tc_commit(&sh->o_full[t]);
       }
       __syncwarp();
+    };
+    auto release = [&](int i) {
+      if (lane == 0) tc_commit(&sh->kv_empty[i % kKvStages]);
+      __syncwarp();
+    };
+
+    if (nt0 > 0) wait(&sh->q_full[0], 0);
+    if (nt1 > 0) wait(&sh->q_full[1], 0);
+    if (wait_kv(0)) {
+      if (nt0 > 0) issue_s(0, 0);
+      if (nt1 > 0) issue_s(1, 0);
+      release(0);
+    }
+    for (int j = 0; ok && j < nmax; ++j) {
+      const int i_v = 2 * j + 1, i_kn = 2 * j + 2;
+      if (!wait_kv(i_v)) break;
+      if (j < nt0) {
+        if (!wait(&sh->p_ready[0], (uint32_t)j & 1u)) break;
+        issue_pv(0, i_v, j == 0, j == nt0 - 1);
+      }
+      if (j + 1 < nt0) {
+        if (!wait_kv(i_kn)) break;
+        issue_s(0, i_kn);
+      }
+      if (j < nt1) {
+        if (!wait(&sh->p_ready[1], (uint32_t)j & 1u)) break;
+        issue_pv(1, i_v, j == 0, j == nt1 - 1);
+      }
+      release(i_v);
+      if (j + 1 < nt1) {
+        if (!wait_kv(i_kn)) break;
+        issue_s(1, i_kn);
+      }
+      if (j + 1 < nmax) release(i_kn);
     }
     if (!ok && lane == 0) sh->aborted = 1;
   } else {
     // ---------------------------------------------------------------- softmax / epilogue -----
-    const int row = warp * 32 + lane;
-    const int qr = m0 + row;
+    const int t = warp >> 2;            // tile of this warpgroup
+    const int quad = warp & 3;          // TMEM lane quadrant this warp may access
+    const int wtid = tid - t * 128;     // thread index inside the warpgroup
+    const TileInfo T = tiles[t];
+    uint8_t *sQt = sQ + t * kTileBytes;
+    const int row = quad * 32 + lane;
+    const int qr = T.m0 + row;
     int lim_row = lk;
     if (p.causal) lim_row = min(lk, qr + 1 + lk - lq);
-    const uint32_t t_s = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const uint32_t t_o = t_s + 128;
+    const uint32_t t_s = tmem_base + t * 128 + ((uint32_t)(quad * 32) << 16);
+    const uint32_t t_o = tmem_base + 256 + t * 128 + ((uint32_t)(quad * 32) << 16);
     const float sc = p.scale_log2e;
     float m_used = -INFINITY, m_next = -INFINITY, l_sum = 0.f;
     bool ok = true, pending = false;
 
-    for (int j = 0; j < n_tiles; ++j) {
-      ok = mbar_wait_abortable(&sh->s_full, (uint32_t)j & 1u, p.status);
+    for (int j = 0; j < T.n_tiles; ++j) {
+      ok = mbar_wait_abortable(&sh->s_full[t], (uint32_t)j & 1u, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -338,18 +428,20 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->p_ready);
+      if (lane == 0) mbar_arrive(&sh->p_ready[t]);
     }
 
+
+    if (T.n_tiles == 0) ok = false;
     if (ok) {
-      ok = mbar_wait_abortable(&sh->o_full, 0, p.status);
+      ok = mbar_wait_abortable(&sh->o_full[t], 0, p.status);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
       tc_fence_after();
       const float inv = l_sum > 0.f ? __fdividef(1.f, l_sum) : 0.f;
       // staging tile [128 rows][128 bf16] over the Q buffer, 16-byte chunks XOR-swizzled by row
-      uint8_t *stage = sQ;
+      uint8_t *stage = sQt;
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t r[32];
@@ -369,16 +461,16 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // the four warps meet on an mbarrier (bounded wait) rather than a hardware barrier, so a
       // warp that unwound early cannot leave the others waiting forever
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->staged);
-      ok = __all_sync(0xffffffffu, mbar_wait(&sh->staged, 0, p.status));
+      if (lane == 0) mbar_arrive(&sh->staged[t]);
+      ok = __all_sync(0xffffffffu, mbar_wait(&sh->staged[t], 0, p.status));
     }
     if (ok) {
-      const uint8_t *stage = sQ;
-      __nv_bfloat16 *obase = p.out + (int64_t)(q0 + m0) * p.o_tok_stride + (int64_t)h * p.o_head_stride;
+      const uint8_t *stage = sQt;
+      __nv_bfloat16 *obase = p.out + (int64_t)(q0 + T.m0) * p.o_tok_stride + (int64_t)T.h * p.o_head_stride;
 #pragma unroll 4
       for (int it = 0; it < 16; ++it) {
-        const int rr = it * 8 + (tid >> 4), chunk = tid & 15;
-        if (rr < rows) {
+        const int rr = it * 8 + (wtid >> 4), chunk = wtid & 15;
+        if (rr < T.rows) {
           const uint4 v = *reinterpret_cast<const uint4 *>(stage + rr * 256 + ((chunk ^ (rr & 7)) << 4));
           *reinterpret_cast<uint4 *>(obase + (int64_t)rr * p.o_tok_stride + chunk * 8) = v;
         }
@@ -389,12 +481,12 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   // ---- teardown ------------------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     if (sh->aborted) {
       // bounded wait for whatever the tensor pipe still owes before the columns are released
-      if (lane == 0) tc_commit(&sh->o_full);
+      if (lane == 0) tc_commit(&sh->drain);
       __syncwarp();
-      mbar_wait(&sh->o_full, 0, p.status);
+      mbar_wait(&sh->drain, 0, p.status);
     }
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -498,7 +590,10 @@ extern "C" char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, co
   p.causal = is_causal ? 1 : 0;
   p.scale_log2e = softmax_scale * 1.4426950408889634f;
   p.status = st;
-  dim3 grid((max_seqlen_q + kBM - 1) / kBM, num_heads, batch);
+  // two tiles per CTA: two heads of one kv group when the group is even, else two row tiles
+  p.pair_heads = (p.group % 2 == 0) ? 1 : 0;
+  const int mblocks = (max_seqlen_q + kBM - 1) / kBM;
+  dim3 grid(p.pair_heads ? mblocks : (mblocks + 1) / 2, p.pair_heads ? num_heads / 2 : num_heads, batch);
   varlen_prefill_kernel<<<grid, kPrefillThreads, kPrefillSmemBytes, static_cast<cudaStream_t>(stream)>>>(
       tq, tk, tv, p);
   AICI_CUDA(cudaGetLastError());
