@@ -116,6 +116,10 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
   }
   __syncwarp();
 
+  // Programmatic dependent launch: let the merge grid get resident early, and (when this grid was
+  // itself launched as a dependent of the plan kernel) wait for the chunk list before reading it.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int n_entries = p.entries != nullptr ? *p.n_entries : p.num_seqs * p.max_parts;
   const int n_items = n_entries * p.num_kv_heads;
   const int stride = gridDim.x * kWarps;
@@ -313,29 +317,55 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
   }
 }
 
-// Combines the chunk partials of one (sequence, head): v2 reduce of the reference.
+// Combines the chunk partials of one (sequence, head): v2 reduce of the reference
+// (attention_kernels.cu:450-546).  One warp per (sequence, head); lane l owns d = 4l .. 4l+3.
+// The weights of up to 32 chunks are computed in parallel, one per lane, and handed round by
+// shuffle, so the row loads of the loop are independent of each other.
+constexpr int kMergeWarps = 4;
 template <typename PartT>
-__global__ void __launch_bounds__(kD) paged_merge_kernel(const DecodeParams p) {
-  const int head = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+__global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const DecodeParams p) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // no-op unless launched as a dependent grid
+  const int lane = threadIdx.x & 31;
+  const int idx = blockIdx.x * kMergeWarps + (threadIdx.x >> 5);
+  if (idx >= p.num_seqs * p.num_heads) return;
+  const int seq = idx / p.num_heads, head = idx - seq * p.num_heads;
   const int ctx = clamp_ctx(p, p.context_lens[seq]);
   const int n = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
   if (n == 1) return;  // the decode kernel wrote the row itself
-  __nv_bfloat16 *dst = p.out + ((int64_t)seq * p.num_heads + head) * kD + d;
+  uint2 *dst = reinterpret_cast<uint2 *>(p.out + ((int64_t)seq * p.num_heads + head) * kD + 4 * lane);
   if (n <= 0) {
-    *dst = __float2bfloat16(0.f);
+    *dst = make_uint2(0u, 0u);
     return;
   }
   const int64_t base = ((int64_t)seq * p.num_heads + head) * p.max_parts;
   float m = -INFINITY;
-  for (int j = 0; j < n; ++j) m = fmaxf(m, p.part_max[base + j]);
-  float wsum = 0.f, acc = 0.f;
-  const PartT *po = static_cast<const PartT *>(p.part_out) + base * kD + d;
-  for (int j = 0; j < n; ++j) {
-    const float w = p.part_sum[base + j] * __expf(p.part_max[base + j] - m);
-    wsum += w;
-    acc += w * static_cast<float>(po[(int64_t)j * kD]);
+  for (int j = lane; j < n; j += 32) m = fmaxf(m, p.part_max[base + j]);
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float wsum = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  const PartT *po = static_cast<const PartT *>(p.part_out) + base * kD + 4 * lane;
+  for (int j0 = 0; j0 < n; j0 += 32) {
+    const int cnt = min(32, n - j0);
+    float w_lane = 0.f;
+    if (lane < cnt) w_lane = p.part_sum[base + j0 + lane] * __expf(p.part_max[base + j0 + lane] - m);
+#pragma unroll 4
+    for (int j = 0; j < cnt; ++j) {
+      const float w = __shfl_sync(0xffffffffu, w_lane, j);
+      wsum += w;
+      if (sizeof(PartT) == 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(po + (int64_t)(j0 + j) * kD);
+        a0 += w * v.x; a1 += w * v.y; a2 += w * v.z; a3 += w * v.w;
+      } else {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(po + (int64_t)(j0 + j) * kD);
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
+        a0 += w * __low2float(lo); a1 += w * __high2float(lo);
+        a2 += w * __low2float(hi); a3 += w * __high2float(hi);
+      }
+    }
   }
-  *dst = __float2bfloat16(acc * __fdividef(1.f, wsum + 1e-6f));
+  const float inv = __fdividef(1.f, wsum + 1e-6f);
+  *dst = make_uint2(pack_bf16(a0 * inv, a1 * inv), pack_bf16(a2 * inv, a3 * inv));
 }
 
 // Builds the compact (seq, chunk) list so that every warp of the decode kernel gets the same
@@ -344,6 +374,7 @@ __global__ void __launch_bounds__(1024) paged_plan_kernel(const DecodeParams p, 
                                                           int *n_entries) {
   __shared__ int s_warp[32];
   __shared__ int s_base;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) s_base = 0;
   __syncthreads();
@@ -482,10 +513,24 @@ static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaS
   const int64_t need = (ub_items + kWarps - 1) / kWarps;
   if (need < grid) grid = (int)need;
   if (grid < 1) grid = 1;
-  paged_decode_kernel<PartT><<<grid, kWarps * 32, smem, stream>>>(p);
-  AICI_CUDA(cudaGetLastError());
-  paged_merge_kernel<PartT><<<dim3(p.num_heads, p.num_seqs), kD, 0, stream>>>(p);
-  AICI_CUDA(cudaGetLastError());
+  // decode and merge are launched as programmatic dependents: their prologues overlap the tail of
+  // the grid before them, and each waits (griddepcontrol.wait) before touching its inputs
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_decode_kernel<PartT>, p));
+  const int rows = p.num_seqs * p.num_heads;
+  cfg.gridDim = dim3((rows + kMergeWarps - 1) / kMergeWarps);
+  cfg.blockDim = dim3(kMergeWarps * 32);
+  cfg.dynamicSmemBytes = 0;
+  AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_merge_kernel<PartT>, p));
   return nullptr;
 }
 
