@@ -29,6 +29,7 @@ constexpr int kStageBytes = 2 * kTileBytes; // key tile + value tile
 constexpr int kWarps = 4;                   // warps per CTA, each with a private ring
 constexpr int kStages = 3;                  // ring depth per warp
 constexpr int kMaxChunk = 512;              // tokens; 32 tiles, one block id per lane
+constexpr int kMaxInlineSeqs = 2048;        // batch size up to which each CTA plans for itself
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -51,6 +52,7 @@ struct DecodeParams {
   int chunk_tokens;
   int max_parts;
   int always_write_partials;  // v2 calling convention: partials are an output too
+  int inline_plan;            // 1: every CTA builds the chunk prefix sums itself (no plan kernel)
   int64_t q_stride, kv_block_stride, kv_head_stride;
   float scale_log2e;
   unsigned int *status;
@@ -72,10 +74,20 @@ __device__ __forceinline__ int clamp_ctx(const DecodeParams &p, int ctx) {
 }
 
 // Decodes work item `idx`; ntiles == 0 marks an empty one (virtual grid only).
-__device__ __forceinline__ void fetch_item(const DecodeParams &p, int idx, Item &it) {
+__device__ __forceinline__ void fetch_item(const DecodeParams &p, const int *s_cum, int idx, Item &it) {
   const int e = idx / p.num_kv_heads;
   it.kvh = idx - e * p.num_kv_heads;
-  if (p.entries != nullptr) {
+  if (p.inline_plan) {
+    // s_cum[i] = number of chunks of sequences < i (shared memory): the sequence is the last i
+    // with s_cum[i] <= e
+    int lo = 0, hi = p.num_seqs;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (s_cum[mid] <= e) lo = mid; else hi = mid;
+    }
+    it.seq = lo;
+    it.chunk = e - s_cum[lo];
+  } else if (p.entries != nullptr) {
     const int2 sc = p.entries[e];
     it.seq = sc.x;
     it.chunk = sc.y;
@@ -120,7 +132,31 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
   // itself launched as a dependent of the plan kernel) wait for the chunk list before reading it.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int n_entries = p.entries != nullptr ? *p.n_entries : p.num_seqs * p.max_parts;
+  int *s_cum = reinterpret_cast<int *>(smem + kWarps * kStages * kStageBytes + kWarps * kStages * sizeof(uint64_t));
+  if (p.inline_plan) {
+    // chunk-count prefix sums over the batch, built by warp 0 of every CTA
+    if (warp == 0) {
+      int carry = 0;
+      for (int s0 = 0; s0 < p.num_seqs; s0 += 32) {
+        const int seq = s0 + lane;
+        int cnt = 0;
+        if (seq < p.num_seqs)
+          cnt = (clamp_ctx(p, p.context_lens[seq]) + p.chunk_tokens - 1) / p.chunk_tokens;
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += v;
+        }
+        if (seq < p.num_seqs) s_cum[seq] = carry + incl - cnt;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) s_cum[p.num_seqs] = carry;
+    }
+    __syncthreads();
+  }
+  const int n_entries = p.inline_plan ? s_cum[p.num_seqs]
+                                      : (p.entries != nullptr ? *p.n_entries : p.num_seqs * p.max_parts);
   const int n_items = n_entries * p.num_kv_heads;
   const int stride = gridDim.x * kWarps;
   const int gw = blockIdx.x * kWarps + warp;
@@ -143,7 +179,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
           p_done = true;
           return;
         }
-        fetch_item(p, p_idx, p_item);
+        fetch_item(p, s_cum, p_idx, p_item);
       } while (p_item.ntiles == 0);
       int b = 0;
       if (lane < p_item.ntiles) {
@@ -189,7 +225,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
     do {
       c_idx += stride;
       if (c_idx >= n_items) break;
-      fetch_item(p, c_idx, it);
+      fetch_item(p, s_cum, c_idx, it);
     } while (it.ntiles == 0);
     if (c_idx >= n_items) break;
 
@@ -318,23 +354,24 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
 }
 
 // Combines the chunk partials of one (sequence, head): v2 reduce of the reference
-// (attention_kernels.cu:450-546).  One warp per (sequence, head); lane l owns d = 4l .. 4l+3.
-// The weights of up to 32 chunks are computed in parallel, one per lane, and handed round by
-// shuffle, so the row loads of the loop are independent of each other.
-constexpr int kMergeWarps = 4;
+// (attention_kernels.cu:450-546).  One CTA of 8 warps per (sequence, head): every warp finds the
+// global maximum, then takes every 8th chunk -- one weight per lane, handed round by shuffle, so
+// the 512-byte row loads of a warp are independent -- and the eight partial sums meet in shared
+// memory.  Lane l owns d = 4l .. 4l+3.
+constexpr int kMergeWarps = 8;
 template <typename PartT>
 __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const DecodeParams p) {
   asm volatile("griddepcontrol.wait;" ::: "memory");  // no-op unless launched as a dependent grid
-  const int lane = threadIdx.x & 31;
-  const int idx = blockIdx.x * kMergeWarps + (threadIdx.x >> 5);
-  if (idx >= p.num_seqs * p.num_heads) return;
-  const int seq = idx / p.num_heads, head = idx - seq * p.num_heads;
+  __shared__ float s_acc[kMergeWarps][kD];
+  __shared__ float s_w[kMergeWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int seq = blockIdx.x / p.num_heads, head = blockIdx.x - seq * p.num_heads;
   const int ctx = clamp_ctx(p, p.context_lens[seq]);
   const int n = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
   if (n == 1) return;  // the decode kernel wrote the row itself
   uint2 *dst = reinterpret_cast<uint2 *>(p.out + ((int64_t)seq * p.num_heads + head) * kD + 4 * lane);
   if (n <= 0) {
-    *dst = make_uint2(0u, 0u);
+    if (warp == 0) *dst = make_uint2(0u, 0u);
     return;
   }
   const int64_t base = ((int64_t)seq * p.num_heads + head) * p.max_parts;
@@ -344,19 +381,24 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const Dec
   for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   float wsum = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
   const PartT *po = static_cast<const PartT *>(p.part_out) + base * kD + 4 * lane;
-  for (int j0 = 0; j0 < n; j0 += 32) {
-    const int cnt = min(32, n - j0);
+  // this warp's chunks: warp, warp + 8, ...; lane l prepares the weight of chunk warp + 8 l
+  for (int j0 = warp; j0 < n; j0 += kMergeWarps * 32) {
+    const int cnt = min(32, (n - j0 + kMergeWarps - 1) / kMergeWarps);
     float w_lane = 0.f;
-    if (lane < cnt) w_lane = p.part_sum[base + j0 + lane] * __expf(p.part_max[base + j0 + lane] - m);
+    if (lane < cnt) {
+      const int j = j0 + kMergeWarps * lane;
+      w_lane = p.part_sum[base + j] * __expf(p.part_max[base + j] - m);
+    }
 #pragma unroll 4
-    for (int j = 0; j < cnt; ++j) {
-      const float w = __shfl_sync(0xffffffffu, w_lane, j);
+    for (int l = 0; l < cnt; ++l) {
+      const float w = __shfl_sync(0xffffffffu, w_lane, l);
+      const int j = j0 + kMergeWarps * l;
       wsum += w;
       if (sizeof(PartT) == 4) {
-        const float4 v = *reinterpret_cast<const float4 *>(po + (int64_t)(j0 + j) * kD);
+        const float4 v = *reinterpret_cast<const float4 *>(po + (int64_t)j * kD);
         a0 += w * v.x; a1 += w * v.y; a2 += w * v.z; a3 += w * v.w;
       } else {
-        const uint2 raw = *reinterpret_cast<const uint2 *>(po + (int64_t)(j0 + j) * kD);
+        const uint2 raw = *reinterpret_cast<const uint2 *>(po + (int64_t)j * kD);
         const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x);
         const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
         a0 += w * __low2float(lo); a1 += w * __high2float(lo);
@@ -364,8 +406,20 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const Dec
       }
     }
   }
-  const float inv = __fdividef(1.f, wsum + 1e-6f);
-  *dst = make_uint2(pack_bf16(a0 * inv, a1 * inv), pack_bf16(a2 * inv, a3 * inv));
+  *reinterpret_cast<float4 *>(&s_acc[warp][4 * lane]) = make_float4(a0, a1, a2, a3);
+  if (lane == 0) s_w[warp] = wsum;
+  __syncthreads();
+  if (warp == 0) {
+    float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f, tw = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMergeWarps; ++w) {
+      const float4 v = *reinterpret_cast<const float4 *>(&s_acc[w][4 * lane]);
+      t0 += v.x; t1 += v.y; t2 += v.z; t3 += v.w;
+      tw += s_w[w];
+    }
+    const float inv = __fdividef(1.f, tw + 1e-6f);
+    *dst = make_uint2(pack_bf16(t0 * inv, t1 * inv), pack_bf16(t2 * inv, t3 * inv));
+  }
 }
 
 // Builds the compact (seq, chunk) list so that every warp of the decode kernel gets the same
@@ -428,10 +482,19 @@ static int sm_count() {
   return cached[dev];
 }
 
-static int pick_chunk(int max_context_len) {
-  (void)max_context_len;
+// Tokens per work item.  256 (16 cache blocks, 128 KB of K+V) keeps the partial-result traffic
+// near 1 %, but a warp streams only about 5 GB/s, so with few (sequence, kv head) pairs per GPU
+// -- heads sharded over many GPUs, or a small batch -- coarse items leave some warps with one
+// item more than others.  The chunk is halved until the upper bound of the item count reaches 16
+// per resident warp (about 8 real items for uniformly drawn contexts), down to 64 tokens.
+static int pick_chunk(int num_seqs, int num_kv_heads, int max_context_len) {
   if (g_chunk_override > 0) return g_chunk_override;
-  return 256;
+  const int64_t warps = (int64_t)2 * sm_count() * kWarps;
+  int chunk = 256;
+  while (chunk > 64 &&
+         (int64_t)num_seqs * ((max_context_len + chunk - 1) / chunk) * num_kv_heads < 16 * warps)
+    chunk >>= 1;
+  return chunk;
 }
 
 constexpr size_t kAlign = 256;
@@ -494,7 +557,8 @@ static char *check_decode_args(const char *fn, const void *out, const void *quer
 template <typename PartT>
 static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaStream_t stream) {
   static bool attr_set[64] = {false};
-  const int smem = kWarps * kStages * kStageBytes + kWarps * kStages * (int)sizeof(uint64_t);
+  const int smem = kWarps * kStages * kStageBytes + kWarps * kStages * (int)sizeof(uint64_t) +
+                   (kMaxInlineSeqs + 1) * (int)sizeof(int);
   int dev = 0;
   AICI_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -502,11 +566,14 @@ static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaS
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[dev] = true;
   }
-  if (entries != nullptr) {
+  // small and medium batches: every CTA plans for itself; very large ones: a plan kernel writes
+  // the compact chunk list into the workspace (v2 convention, no workspace: virtual grid)
+  p.inline_plan = (entries != nullptr && p.num_seqs <= kMaxInlineSeqs) ? 1 : 0;
+  if (entries != nullptr && !p.inline_plan) {
     paged_plan_kernel<<<1, 1024, 0, stream>>>(p, entries, n_entries);
     AICI_CUDA(cudaGetLastError());
   }
-  p.entries = entries;
+  p.entries = p.inline_plan ? nullptr : entries;
   p.n_entries = n_entries;
   const int64_t ub_items = (int64_t)p.num_seqs * p.max_parts * p.num_kv_heads;
   int grid = 2 * sm_count();
@@ -526,8 +593,7 @@ static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaS
   cfg.blockDim = dim3(kWarps * 32);
   cfg.dynamicSmemBytes = smem;
   AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_decode_kernel<PartT>, p));
-  const int rows = p.num_seqs * p.num_heads;
-  cfg.gridDim = dim3((rows + kMergeWarps - 1) / kMergeWarps);
+  cfg.gridDim = dim3(p.num_seqs * p.num_heads);
   cfg.blockDim = dim3(kMergeWarps * 32);
   cfg.dynamicSmemBytes = 0;
   AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_merge_kernel<PartT>, p));
@@ -547,10 +613,11 @@ extern "C" char *aici_tune_decode_chunk(int chunk_tokens) {
   return nullptr;
 }
 
-extern "C" size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads,
+extern "C" size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads, int num_kv_heads,
                                                        int max_context_len) {
-  if (num_seqs <= 0 || num_heads <= 0) return kAlign;
-  return workspace_layout(num_seqs, num_heads, max_context_len, pick_chunk(max_context_len)).total;
+  if (num_seqs <= 0 || num_heads <= 0 || num_kv_heads <= 0) return kAlign;
+  return workspace_layout(num_seqs, num_heads, max_context_len,
+                          pick_chunk(num_seqs, num_kv_heads, max_context_len)).total;
 }
 
 extern "C" char *aici_paged_attention_v1(void *out, const void *query, const void *key_cache,
@@ -571,7 +638,7 @@ extern "C" char *aici_paged_attention_v1(void *out, const void *query, const voi
                                   kv_head_stride, dtype))
     return e;
   if (num_seqs == 0) return nullptr;
-  const int chunk = pick_chunk(max_context_len);
+  const int chunk = pick_chunk(num_seqs, num_kv_heads, max_context_len);
   const WorkspaceLayout w = workspace_layout(num_seqs, num_heads, max_context_len, chunk);
   AICI_CHECK(workspace != nullptr && workspace_bytes >= w.total,
              "%s: workspace too small (%zu bytes given, %zu needed)", fn, workspace_bytes, w.total);
@@ -700,7 +767,8 @@ extern "C" char *aici_paged_attention_v1_static(
     scratch_addr[dev] = p;
   }
   if (num_seqs > 0 && num_heads > 0) {
-    const size_t need = aici_paged_attention_workspace_bytes(num_seqs, num_heads, max_context_len);
+    const size_t need =
+        aici_paged_attention_workspace_bytes(num_seqs, num_heads, num_kv_heads, max_context_len);
     AICI_CHECK(need <= kStaticScratchBytes,
                "%s: this batch needs %zu bytes of scratch but the built-in array holds %zu "
                "(num_seqs * ceil(max_context_len / chunk) * num_heads is too large); use "

@@ -288,7 +288,8 @@ def paged_attention_v1(out: torch.Tensor, query: torch.Tensor, key_cache: torch.
     L = _lib.lib()
     with torch.cuda.device(dev):
         nbytes = L.aici_paged_attention_workspace_bytes(
-            ctypes.c_int(num_seqs), ctypes.c_int(num_heads), ctypes.c_int(int(max_context_len)))
+            ctypes.c_int(num_seqs), ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads),
+            ctypes.c_int(int(max_context_len)))
         ws = _workspace(dev, nbytes)
         res = L.aici_paged_attention_v1(
             _p(out), _p(query), _p(key_cache), _p(value_cache), ctypes.c_int(num_kv_heads),

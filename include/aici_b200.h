@@ -87,8 +87,10 @@ char *aici_copy_blocks_host(const int64_t *key_cache_ptrs_host,
 
 /* ---- decode attention over the paged cache ----------------------------------------- */
 
-/* Bytes of caller-owned scratch aici_paged_attention_v1 needs for these sizes. */
-size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads, int max_context_len);
+/* Bytes of caller-owned scratch aici_paged_attention_v1 needs for these sizes (the chunk size of
+ * the context split, and with it the number of partial results, depends on all four). */
+size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads, int num_kv_heads,
+                                            int max_context_len);
 
 /* Replaces paged_attention_v1_C (lib.rs:108-120; vllm_bindings.cpp:17-29;
  * kernels/vllm/attention/attention_kernels.cu:571-700).  out/query

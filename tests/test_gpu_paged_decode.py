@@ -70,6 +70,18 @@ def test_strided_query_rows(cuda_device):
     _check(out.cpu(), O.paged_attention_v1(q, kc, vc, 2, 0.1, bt, cl))
 
 
+def test_large_batch_uses_the_plan_kernel(cuda_device):
+    """More than 2048 sequences: the chunk list is built by a separate kernel into the workspace."""
+    g = torch.Generator().manual_seed(350)
+    ctx = torch.randint(1, 300, (2100,), generator=g).tolist()
+    ctx[7] = 0
+    q, kc, vc, bt, cl = _case(351, 8, 2, ctx, sum((c + 15) // 16 for c in ctx) + 4)
+    got = _run_v1(cuda_device, q, kc, vc, 2, 0.088, bt, cl)
+    _check(got, O.paged_attention_v1(q, kc, vc, 2, 0.088, bt, cl))
+    assert float(got[7].float().abs().max()) == 0.0
+    assert _lib.last_status() == 0
+
+
 @pytest.mark.parametrize("chunk", [16, 64, 512])
 def test_chunk_sizes(cuda_device, chunk):
     ctx = [700, 16, 1, 2049, 130]

@@ -45,7 +45,7 @@ def test_static_scratch_entry_point_matches_twice_in_a_row(cuda_device):
 
 def test_static_scratch_entry_point_refuses_oversized_batches(cuda_device):
     need = _lib.lib().aici_paged_attention_workspace_bytes(ctypes.c_int(256), ctypes.c_int(32),
-                                                           ctypes.c_int(8192))
+                                                           ctypes.c_int(8), ctypes.c_int(8192))
     assert need > (32 << 20)
     w = workloads.make_decode("c", cuda_device, num_seqs=2, num_heads=8, num_kv_heads=8,
                               ctx_kind="uniform", ctx_lo=20, ctx_hi=40, pool_blocks=16, seed=912)
