@@ -23,6 +23,7 @@ EXPORTS = (
     "aici_paged_attention_v2",
     "aici_paged_attention_v1_static",
     "aici_mha_varlen_fwd",
+    "aici_mha_varlen_paged_fwd",
 )
 
 _lib = None

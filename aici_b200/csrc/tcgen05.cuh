@@ -53,6 +53,15 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
          ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// Same descriptor with an explicit swizzle mode: 0 = none (core matrices of 8 rows x 16 bytes,
+// leading offset = distance between the two core matrices of one K step, stride offset = distance
+// between 8-row groups), 6 = 32-byte swizzle, 4 = 64-byte, 2 = 128-byte.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t swizzle_mode) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
+         ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | ((uint64_t)swizzle_mode << 61);
+}
+
 // Instruction descriptor for kind::f16: fp32 accumulate, bf16 A and B, A K-major.
 //   bits [4,6) D format (1 = f32)   [7,10) A format (1 = bf16)   [10,13) B format (1 = bf16)
 //   bit 15 A major   bit 16 B major (0 = K, 1 = MN)   [17,23) N >> 3   [24,29) M >> 4
@@ -133,6 +142,24 @@ __device__ __forceinline__ void tma_load_3d(void *dst_smem, const CUtensorMap *t
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
       "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst_smem)),
       "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(void *dst_smem, const CUtensorMap *tmap, int c0, int c1,
+                                            int c2, int c3, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(dst_smem)),
+      "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(void *dst_smem, const CUtensorMap *tmap, int c0, int c1,
+                                            int c2, int c3, int c4, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(smem_u32(dst_smem)),
+      "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
 

@@ -47,6 +47,11 @@ struct PrefillParams {
   int pair_heads;  // 1: the two tiles are heads 2y and 2y+1; 0: two consecutive row tiles of head y
   float scale_log2e;
   unsigned int *status;
+  // paged variant: keys/values are read from the KV cache through the block table
+  const int32_t *block_tables;  // [batch, max_blocks]
+  const int32_t *k_lens;        // [batch] tokens of each sequence present in the cache
+  int max_blocks;
+  int64_t num_blocks;
 };
 
 struct PrefillSmem {
@@ -73,6 +78,14 @@ __device__ __forceinline__ void zero_rows(const PrefillParams &p, int q0, const 
   }
 }
 
+// kPaged = false: K and V are packed [total_k, Hkv, 128] tensors (tensor maps as for Q).
+// kPaged = true : K and V come from the paged cache.  A key tile is 16 half-blocks of
+//   [16 chunks][8 tokens][8 elements] (2 KB each, no swizzle: exactly the 8-row x 16-byte core
+//   matrices the MMA wants, leading offset 128 B between the two chunks of a K step, stride offset
+//   2 KB between 8-token groups); a value tile is 8 blocks of [128 d][16 tokens] loaded with the
+//   32-byte swizzle, one K = 16 MMA per block.  Value columns past the sequence end are zeroed in
+//   shared memory before P V (cache slots there may hold anything, NaN included).
+template <bool kPaged>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
@@ -81,7 +94,18 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.z;
   const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
-  const int k0 = p.cu_k[b], lk = p.cu_k[b + 1] - k0;
+  int k0 = 0, lk = 0;
+  if (kPaged) {
+    lk = p.k_lens[b];
+    if (lk > p.max_blocks * 16) {
+      if (tid == 0) set_status(p.status, AICI_STATUS_BAD_BLOCK);
+      lk = p.max_blocks * 16;
+    }
+    if (lk < 0) lk = 0;
+  } else {
+    k0 = p.cu_k[b];
+    lk = p.cu_k[b + 1] - k0;
+  }
   const int n_mblocks = (lq + kBM - 1) / kBM;
 
   // ---- which two tiles does this CTA own? (longest causal tiles are scheduled first) ----------
@@ -173,16 +197,43 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const int stage = i % kKvStages;
         if (!mbar_wait_abortable(&sh->kv_empty[stage], (((uint32_t)i / kKvStages) & 1u) ^ 1u, p.status)) break;
         uint8_t *dst = sKV + stage * kTileBytes;
-        const CUtensorMap *tm = (i & 1) ? &tmap_v : &tmap_k;
-        mbar_expect_tx(&sh->kv_full[stage], kTileBytes);
-        tma_load_3d(dst, tm, 0, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
-        tma_load_3d(dst + kPanelBytes, tm, 64, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
+        if (kPaged) {
+          const int j = i >> 1;
+          const int nb = min(8, (lk - j * kBN + 15) / 16);  // cache blocks of this tile that exist
+          const int32_t *bt = p.block_tables + (int64_t)b * p.max_blocks + j * 8;
+          int blk[8];
+#pragma unroll
+          for (int bi = 0; bi < 8; ++bi) {
+            blk[bi] = bi < nb ? bt[bi] : 0;
+            if (blk[bi] < 0 || blk[bi] >= p.num_blocks) {
+              set_status(p.status, AICI_STATUS_BAD_BLOCK);
+              blk[bi] = 0;
+            }
+          }
+          mbar_expect_tx(&sh->kv_full[stage], nb * 4096);
+#pragma unroll
+          for (int bi = 0; bi < 8; ++bi) {
+            if (bi < nb) {
+              if (i & 1) {
+                tma_load_4d(dst + bi * 4096, &tmap_v, 0, 0, hk, blk[bi], &sh->kv_full[stage]);
+              } else {
+                tma_load_5d(dst + bi * 4096, &tmap_k, 0, 0, 0, hk, blk[bi], &sh->kv_full[stage]);
+                tma_load_5d(dst + bi * 4096 + 2048, &tmap_k, 0, 8, 0, hk, blk[bi], &sh->kv_full[stage]);
+              }
+            }
+          }
+        } else {
+          const CUtensorMap *tm = (i & 1) ? &tmap_v : &tmap_k;
+          mbar_expect_tx(&sh->kv_full[stage], kTileBytes);
+          tma_load_3d(dst, tm, 0, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
+          tma_load_3d(dst + kPanelBytes, tm, 64, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
+        }
       }
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer -------------
     constexpr uint32_t idesc_s = idesc_bf16(kBM, kBN, false);
-    constexpr uint32_t idesc_pv = idesc_bf16(kBM, kHD, true);
+    constexpr uint32_t idesc_pv = idesc_bf16(kBM, kHD, !kPaged);  // packed V: MN-major; cache V: K-major
     bool ok = true;
     auto wait = [&](uint64_t *bar, uint32_t parity) {
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait_abortable(bar, parity, p.status));
@@ -194,11 +245,13 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       tc_fence_after();
       if (lane == 0) {
         const uint64_t qdesc = smem_desc_sw128(smem_u32(sQ + t * kTileBytes), 16, 1024);
-        const uint64_t kdesc = smem_desc_sw128(smem_u32(sKV + (i_k % kKvStages) * kTileBytes), 16, 1024);
+        const uint32_t kaddr = smem_u32(sKV + (i_k % kKvStages) * kTileBytes);
+        const uint64_t kdesc = kPaged ? smem_desc(kaddr, 128, 2048, 0) : smem_desc_sw128(kaddr, 16, 1024);
 #pragma unroll
         for (int ks = 0; ks < kHD / 16; ++ks) {
           const uint64_t adv = (uint64_t)(((ks >> 2) * kPanelBytes + (ks & 3) * 32) >> 4);
-          umma_ss(tmem_base + t * 128, qdesc + adv, kdesc + adv, idesc_s, ks > 0 ? 1u : 0u);
+          const uint64_t kadv = kPaged ? (uint64_t)((ks * 256) >> 4) : adv;
+          umma_ss(tmem_base + t * 128, qdesc + adv, kdesc + kadv, idesc_s, ks > 0 ? 1u : 0u);
         }
         tc_commit(&sh->s_full[t]);
       }
@@ -209,10 +262,14 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     auto issue_pv = [&](int t, int i_v, bool first, bool last) {
       tc_fence_after();
       if (lane == 0) {
-        const uint64_t vdesc = smem_desc_sw128(smem_u32(sKV + (i_v % kKvStages) * kTileBytes), kPanelBytes, 1024);
+        const uint32_t vaddr = smem_u32(sKV + (i_v % kKvStages) * kTileBytes);
+        // packed: one MN-major tile, a K step = 16 token rows of 128 B; cache: one block per K step,
+        // rows (d) of 32 B with the 32-byte swizzle, 8-row groups 256 B apart
+        const uint64_t vdesc = kPaged ? smem_desc(vaddr, 16, 256, 6) : smem_desc_sw128(vaddr, kPanelBytes, 1024);
+        const uint32_t vstep = kPaged ? 4096u : 2048u;
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks)
-          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + 8 * ks, vdesc + (uint64_t)((ks * 2048) >> 4),
+          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + 8 * ks, vdesc + (uint64_t)((ks * vstep) >> 4),
                   idesc_pv, (!first || ks > 0) ? 1u : 0u);
         if (last) tc_commit(&sh->o_full[t]);
       }
@@ -233,6 +290,25 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     for (int j = 0; ok && j < nmax; ++j) {
       const int i_v = 2 * j + 1, i_kn = 2 * j + 2;
       if (!wait_kv(i_v)) break;
+      if (kPaged && lk - j * kBN < kBN) {
+        // last tile of the sequence: zero the value columns of tokens >= lk (generic-proxy stores,
+        // made visible to the tensor core with a proxy fence)
+        const int valid = lk - j * kBN;
+        uint8_t *vt = sKV + (i_v % kKvStages) * kTileBytes;
+        for (int bi = valid / 16; bi < 8; ++bi) {
+          uint8_t *vb = vt + bi * 4096;
+          const int first = max(0, valid - bi * 16);
+          if (first == 0) {
+            for (int idx = lane; idx < 256; idx += 32) reinterpret_cast<uint4 *>(vb)[idx] = make_uint4(0, 0, 0, 0);
+          } else {
+            for (int d = lane; d < kHD; d += 32)
+              for (int tok = first; tok < 16; ++tok)
+                *reinterpret_cast<uint16_t *>(vb + d * 32 + ((((tok >> 3) ^ ((d >> 2) & 1))) << 4) + (tok & 7) * 2) = 0;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
       if (j < nt0) {
         if (!wait(&sh->p_ready[0], (uint32_t)j & 1u)) break;
         issue_pv(0, i_v, j == 0, j == nt0 - 1);
@@ -511,19 +587,48 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// Generic tiled map over bf16 data: dims/box innermost first, strides (bytes) for dims 1..rank-1.
+static char *make_tmap_nd(const char *fn, CUtensorMap *map, const void *base, int rank,
+                          const cuuint64_t *dims, const cuuint64_t *strides, const cuuint32_t *box,
+                          CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn enc = encode_fn();
+  AICI_CHECK(enc != nullptr, "%s: cuTensorMapEncodeTiled is not available from the driver", fn);
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void *>(base), dims,
+                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  AICI_CHECK(r == CUDA_SUCCESS, "%s: cuTensorMapEncodeTiled failed with code %d", fn, (int)r);
+  return nullptr;
+}
+
 // [tokens, heads, 128] bf16 with element strides -> 3-D map, box = 64 (d) x 1 (head) x 128 (tokens).
 static char *make_tmap(const char *fn, CUtensorMap *map, const void *base, int64_t tokens, int heads,
                        int64_t tok_stride, int64_t head_stride) {
-  EncodeTiledFn enc = encode_fn();
-  AICI_CHECK(enc != nullptr, "%s: cuTensorMapEncodeTiled is not available from the driver", fn);
   cuuint64_t dims[3] = {(cuuint64_t)kHD, (cuuint64_t)heads, (cuuint64_t)tokens};
   cuuint64_t strides[2] = {(cuuint64_t)head_stride * 2, (cuuint64_t)tok_stride * 2};
   cuuint32_t box[3] = {64, 1, (cuuint32_t)kBM};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  AICI_CHECK(r == CUDA_SUCCESS, "%s: cuTensorMapEncodeTiled failed with code %d", fn, (int)r);
+  return make_tmap_nd(fn, map, base, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+template <bool kPaged>
+static char *launch_prefill(const char *fn, const CUtensorMap &tq, const CUtensorMap &tk,
+                            const CUtensorMap &tv, PrefillParams &p, int num_heads, int batch,
+                            int max_seqlen_q, cudaStream_t stream) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  AICI_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    AICI_CUDA(cudaFuncSetAttribute(varlen_prefill_kernel<kPaged>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmemBytes));
+    attr_set[dev] = true;
+  }
+  // two tiles per CTA: two heads of one kv group when the group is even, else two row tiles
+  p.pair_heads = (p.group % 2 == 0) ? 1 : 0;
+  const int mblocks = (max_seqlen_q + kBM - 1) / kBM;
+  dim3 grid(p.pair_heads ? mblocks : (mblocks + 1) / 2, p.pair_heads ? num_heads / 2 : num_heads, batch);
+  varlen_prefill_kernel<kPaged><<<grid, kPrefillThreads, kPrefillSmemBytes, stream>>>(tq, tk, tv, p);
+  AICI_CUDA(cudaGetLastError());
+  (void)fn;
   return nullptr;
 }
 
@@ -572,14 +677,6 @@ extern "C" char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, co
   if (char *e = make_tmap(fn, &tk, kk, tk_rows, num_heads_k, k_tok_stride, k_head_stride)) return e;
   if (char *e = make_tmap(fn, &tv, vv, tk_rows, num_heads_k, v_tok_stride, v_head_stride)) return e;
 
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  AICI_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    AICI_CUDA(cudaFuncSetAttribute(varlen_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   kPrefillSmemBytes));
-    attr_set[dev] = true;
-  }
   PrefillParams p;
   p.out = static_cast<__nv_bfloat16 *>(out);
   p.cu_q = cu_seqlens_q;
@@ -590,12 +687,81 @@ extern "C" char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, co
   p.causal = is_causal ? 1 : 0;
   p.scale_log2e = softmax_scale * 1.4426950408889634f;
   p.status = st;
-  // two tiles per CTA: two heads of one kv group when the group is even, else two row tiles
-  p.pair_heads = (p.group % 2 == 0) ? 1 : 0;
-  const int mblocks = (max_seqlen_q + kBM - 1) / kBM;
-  dim3 grid(p.pair_heads ? mblocks : (mblocks + 1) / 2, p.pair_heads ? num_heads / 2 : num_heads, batch);
-  varlen_prefill_kernel<<<grid, kPrefillThreads, kPrefillSmemBytes, static_cast<cudaStream_t>(stream)>>>(
-      tq, tk, tv, p);
-  AICI_CUDA(cudaGetLastError());
-  return nullptr;
+  p.block_tables = nullptr;
+  p.k_lens = nullptr;
+  p.max_blocks = 0;
+  p.num_blocks = 0;
+  return launch_prefill<false>(fn, tq, tk, tv, p, num_heads, batch, max_seqlen_q,
+                               static_cast<cudaStream_t>(stream));
+}
+
+extern "C" char *aici_mha_varlen_paged_fwd(void *out, const void *q, const void *key_cache,
+                                           const void *value_cache, const int32_t *cu_seqlens_q,
+                                           const int32_t *context_lens, const int32_t *block_tables,
+                                           int batch, int total_q, int num_heads, int num_kv_heads,
+                                           int head_size, int block_size, int max_seqlen_q,
+                                           int max_context_len, int max_num_blocks_per_seq,
+                                           int64_t num_blocks, int64_t q_tok_stride,
+                                           int64_t q_head_stride, int64_t o_tok_stride,
+                                           int64_t o_head_stride, int64_t kv_block_stride,
+                                           int64_t kv_head_stride, float softmax_scale, int is_causal,
+                                           int dtype, aici_stream_t stream) {
+  const char *fn = "aici_mha_varlen_paged_fwd";
+  AICI_CHECK(dtype == AICI_DTYPE_BF16, "%s: only bf16 is supported (dtype=%d)", fn, dtype);
+  AICI_CHECK(batch > 0, "%s: batch size must be positive", fn);
+  AICI_CHECK(head_size == kHD, "%s: head_size must be 128 (got %d)", fn, head_size);
+  AICI_CHECK(block_size == 16, "%s: block_size must be 16 (got %d)", fn, block_size);
+  AICI_CHECK(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0,
+             "%s: Number of heads in key/value must divide number of heads in query", fn);
+  AICI_CHECK(total_q >= 0 && max_seqlen_q >= 0 && max_context_len >= 0 && max_num_blocks_per_seq >= 0,
+             "%s: negative size", fn);
+  AICI_CHECK(softmax_scale > 0.f, "%s: softmax_scale must be positive", fn);
+  AICI_CHECK(batch <= 65535 && num_heads <= 65535, "%s: batch and num_heads must fit a grid dimension", fn);
+  if (total_q == 0 || max_seqlen_q == 0) return nullptr;
+  AICI_CHECK(out && q && key_cache && value_cache && cu_seqlens_q && context_lens && block_tables,
+             "%s: NULL pointer", fn);
+  AICI_CHECK(num_blocks > 0, "%s: num_blocks must be positive", fn);
+  AICI_CHECK(((uintptr_t)out | (uintptr_t)q | (uintptr_t)key_cache | (uintptr_t)value_cache) % 16 == 0,
+             "%s: tensors must be 16-byte aligned", fn);
+  const int64_t strides[4] = {q_tok_stride, q_head_stride, o_tok_stride, o_head_stride};
+  for (int i = 0; i < 4; ++i)
+    AICI_CHECK(strides[i] >= kHD && strides[i] % 8 == 0,
+               "%s: token and head strides must be multiples of 8 elements and at least head_size", fn);
+  AICI_CHECK(kv_head_stride == kHD * 16 && kv_block_stride % 8 == 0 &&
+                 kv_block_stride >= (int64_t)num_kv_heads * kHD * 16,
+             "%s: cache must be [blocks, kv_heads, 128/8, 16, 8] with contiguous head tiles", fn);
+  unsigned int *st = status_ptr();
+  AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
+
+  CUtensorMap tq, tk, tv;
+  if (char *e = make_tmap(fn, &tq, q, total_q, num_heads, q_tok_stride, q_head_stride)) return e;
+  {  // key cache [blk][h][c = 16][tok = 16][e = 8]: box = one half block (8 tokens of all chunks)
+    cuuint64_t dims[5] = {8, 16, 16, (cuuint64_t)num_kv_heads, (cuuint64_t)num_blocks};
+    cuuint64_t str[4] = {16, 256, (cuuint64_t)kv_head_stride * 2, (cuuint64_t)kv_block_stride * 2};
+    cuuint32_t box[5] = {8, 8, 16, 1, 1};
+    if (char *e = make_tmap_nd(fn, &tk, key_cache, 5, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+  }
+  {  // value cache [blk][h][d = 128][tok = 16]: box = one block, rows of 32 bytes, 32-byte swizzle
+    cuuint64_t dims[4] = {16, 128, (cuuint64_t)num_kv_heads, (cuuint64_t)num_blocks};
+    cuuint64_t str[3] = {32, (cuuint64_t)kv_head_stride * 2, (cuuint64_t)kv_block_stride * 2};
+    cuuint32_t box[4] = {16, 128, 1, 1};
+    if (char *e = make_tmap_nd(fn, &tv, value_cache, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_32B)) return e;
+  }
+  PrefillParams p;
+  p.out = static_cast<__nv_bfloat16 *>(out);
+  p.cu_q = cu_seqlens_q;
+  p.cu_k = nullptr;
+  p.o_tok_stride = o_tok_stride;
+  p.o_head_stride = o_head_stride;
+  p.group = num_heads / num_kv_heads;
+  p.causal = is_causal ? 1 : 0;
+  p.scale_log2e = softmax_scale * 1.4426950408889634f;
+  p.status = st;
+  p.block_tables = block_tables;
+  p.k_lens = context_lens;
+  p.max_blocks = max_num_blocks_per_seq;
+  p.num_blocks = num_blocks;
+  (void)max_context_len;
+  return launch_prefill<true>(fn, tq, tk, tv, p, num_heads, batch, max_seqlen_q,
+                              static_cast<cudaStream_t>(stream));
 }

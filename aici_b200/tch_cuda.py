@@ -363,3 +363,45 @@ def paged_attention_v1_static(out: torch.Tensor, query: torch.Tensor, key_cache:
             ctypes.c_int64(key_cache.stride(0)), ctypes.c_int64(key_cache.stride(1)),
             ctypes.c_int(_dtype(fn, query)), _stream(dev))
     _lib.check(fn, res)
+
+
+def flash_attn_varlen_paged(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                            seqlens_q: torch.Tensor, context_lens: torch.Tensor,
+                            block_tables: torch.Tensor, max_seqlen_q: int, max_context_len: int,
+                            softmax_scale: float, causal: bool) -> torch.Tensor:
+    """Prefill attention with keys/values read from the paged cache through block tables: what
+    compute_varlen_attn (rllm-cuda/src/llm/mod.rs:168-278) gets from gather_cached_kv + repeat_kv +
+    flash_attn_varlen, without the gathered copy.  `seqlens_q` cumulative int32 [batch + 1];
+    `context_lens` int32 [batch] (tokens of each sequence in the cache, new ones included);
+    `block_tables` int32 [batch, max_blocks].  Returns [total_q, num_heads, head_size]."""
+    fn = "flash_attn_varlen_paged"
+    dev = _require_cuda(fn, q, key_cache, value_cache, seqlens_q, context_lens, block_tables)
+    num_blocks, num_kv_heads, head_size, block_size = _cache_dims(fn, key_cache, value_cache)
+    if q.dim() != 3 or q.shape[2] != head_size or q.stride(2) != 1:
+        raise AiciError("%s: q must be [total_q, num_heads, head_size] with contiguous last dimension" % fn)
+    for t in (seqlens_q, context_lens, block_tables):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise AiciError("%s: seqlens_q, context_lens and block_tables must be contiguous int32" % fn)
+    batch = seqlens_q.numel() - 1
+    if batch <= 0:
+        raise AiciError("%s: batch size must be positive" % fn)
+    if context_lens.numel() != batch or block_tables.dim() != 2 or block_tables.shape[0] != batch:
+        raise AiciError("%s: context_lens must be [batch] and block_tables [batch, max_blocks]" % fn)
+    if q.dtype != key_cache.dtype:
+        raise AiciError("%s: query and cache dtypes differ" % fn)
+    total_q, num_heads, _ = q.shape
+    out = torch.empty((total_q, num_heads, head_size), dtype=q.dtype, device=dev)
+    with torch.cuda.device(dev):
+        res = _lib.lib().aici_mha_varlen_paged_fwd(
+            _p(out), _p(q), _p(key_cache), _p(value_cache), _p(seqlens_q), _p(context_lens),
+            _p(block_tables), ctypes.c_int(batch), ctypes.c_int(total_q), ctypes.c_int(num_heads),
+            ctypes.c_int(num_kv_heads), ctypes.c_int(head_size), ctypes.c_int(block_size),
+            ctypes.c_int(int(max_seqlen_q)), ctypes.c_int(int(max_context_len)),
+            ctypes.c_int(block_tables.shape[1]), ctypes.c_int64(num_blocks),
+            ctypes.c_int64(q.stride(0)), ctypes.c_int64(q.stride(1)),
+            ctypes.c_int64(out.stride(0)), ctypes.c_int64(out.stride(1)),
+            ctypes.c_int64(key_cache.stride(0)), ctypes.c_int64(key_cache.stride(1)),
+            ctypes.c_float(softmax_scale), ctypes.c_int(1 if causal else 0),
+            ctypes.c_int(_dtype(fn, q)), _stream(dev))
+    _lib.check(fn, res)
+    return out

@@ -161,6 +161,25 @@ char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, const void *v
                           int64_t o_tok_stride, int64_t o_head_stride, float softmax_scale,
                           int is_causal, int dtype, aici_stream_t stream);
 
+/* Variable-length causal prefill that reads keys and values straight from the paged cache.
+ * Replaces the sequence gather_cached_kv -> repeat_kv -> flash_attn_varlen of
+ * compute_varlen_attn (rllm-cuda/src/llm/mod.rs:168-278; kernels/vllm/cache_kernels.cu:301-413):
+ * no packed copy of the context is made and no head is replicated.  q/out as in
+ * aici_mha_varlen_fwd; sequence i attends to its first context_lens[i] tokens, found through row i
+ * of block_tables (int32 [batch, max_num_blocks_per_seq]; logical token t lives in block
+ * table[t / 16] at offset t % 16, as rLLM allocates, paged/blocks.rs:122-127).  The causal mask is
+ * bottom-right aligned, so a chunk of new tokens after an already cached prefix is
+ * len_q < context_len.  Cache slots past context_lens[i] may hold anything. */
+char *aici_mha_varlen_paged_fwd(void *out, const void *q, const void *key_cache,
+                                const void *value_cache, const int32_t *cu_seqlens_q,
+                                const int32_t *context_lens, const int32_t *block_tables, int batch,
+                                int total_q, int num_heads, int num_kv_heads, int head_size,
+                                int block_size, int max_seqlen_q, int max_context_len,
+                                int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_tok_stride,
+                                int64_t q_head_stride, int64_t o_tok_stride, int64_t o_head_stride,
+                                int64_t kv_block_stride, int64_t kv_head_stride, float softmax_scale,
+                                int is_causal, int dtype, aici_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
