@@ -193,41 +193,56 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       &sh->q_full[t]);
         }
       }
+    }
+    if (kPaged) {
+      // All lanes take part: lane l < 8 owns cache block l of the tile (its id is read once per
+      // tile, one tile ahead), lanes 0-15 each issue one half-block key copy, lanes 0-7 one value
+      // copy; lane 0 posts the expected byte count.
+      const int32_t *bt_row = p.block_tables + (int64_t)b * p.max_blocks;
+      auto load_id = [&](int j) {
+        int id = 0;
+        const int nb = min(8, (lk - j * kBN + 15) / 16);
+        if ((lane & 7) < nb && j < nmax) {
+          id = bt_row[j * 8 + (lane & 7)];
+          if (id < 0 || id >= p.num_blocks) {
+            set_status(p.status, AICI_STATUS_BAD_BLOCK);
+            id = 0;
+          }
+        }
+        return id;
+      };
+      int id_cur = load_id(0), id_next = 0;
+      bool ok = true;
+      for (int i = 0; ok && i < 2 * nmax; ++i) {  // i even: K_{i/2}, i odd: V_{i/2}
+        const int stage = i % kKvStages;
+        const int j = i >> 1;
+        if (!(i & 1)) id_next = load_id(j + 1);
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait_abortable(&sh->kv_empty[stage], (((uint32_t)i / kKvStages) & 1u) ^ 1u, p.status));
+        if (!ok) break;
+        uint8_t *dst = sKV + stage * kTileBytes;
+        const int nb = min(8, (lk - j * kBN + 15) / 16);  // cache blocks of this tile that exist
+        if (lane == 0) mbar_expect_tx(&sh->kv_full[stage], nb * 4096);
+        const int bi = lane & 7;
+        if (i & 1) {
+          if (lane < 8 && bi < nb) tma_load_4d(dst + bi * 4096, &tmap_v, 0, 0, hk, id_cur, &sh->kv_full[stage]);
+          id_cur = id_next;
+        } else {
+          if (lane < 16 && bi < nb)
+            tma_load_5d(dst + bi * 4096 + (lane >> 3) * 2048, &tmap_k, 0, (lane >> 3) * 8, 0, hk, id_cur,
+                        &sh->kv_full[stage]);
+        }
+        __syncwarp();
+      }
+    } else if (lane == 0) {
       for (int i = 0; i < 2 * nmax; ++i) {  // i even: K_{i/2}, i odd: V_{i/2}
         const int stage = i % kKvStages;
         if (!mbar_wait_abortable(&sh->kv_empty[stage], (((uint32_t)i / kKvStages) & 1u) ^ 1u, p.status)) break;
         uint8_t *dst = sKV + stage * kTileBytes;
-        if (kPaged) {
-          const int j = i >> 1;
-          const int nb = min(8, (lk - j * kBN + 15) / 16);  // cache blocks of this tile that exist
-          const int32_t *bt = p.block_tables + (int64_t)b * p.max_blocks + j * 8;
-          int blk[8];
-#pragma unroll
-          for (int bi = 0; bi < 8; ++bi) {
-            blk[bi] = bi < nb ? bt[bi] : 0;
-            if (blk[bi] < 0 || blk[bi] >= p.num_blocks) {
-              set_status(p.status, AICI_STATUS_BAD_BLOCK);
-              blk[bi] = 0;
-            }
-          }
-          mbar_expect_tx(&sh->kv_full[stage], nb * 4096);
-#pragma unroll
-          for (int bi = 0; bi < 8; ++bi) {
-            if (bi < nb) {
-              if (i & 1) {
-                tma_load_4d(dst + bi * 4096, &tmap_v, 0, 0, hk, blk[bi], &sh->kv_full[stage]);
-              } else {
-                tma_load_5d(dst + bi * 4096, &tmap_k, 0, 0, 0, hk, blk[bi], &sh->kv_full[stage]);
-                tma_load_5d(dst + bi * 4096 + 2048, &tmap_k, 0, 8, 0, hk, blk[bi], &sh->kv_full[stage]);
-              }
-            }
-          }
-        } else {
-          const CUtensorMap *tm = (i & 1) ? &tmap_v : &tmap_k;
-          mbar_expect_tx(&sh->kv_full[stage], kTileBytes);
-          tma_load_3d(dst, tm, 0, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
-          tma_load_3d(dst + kPanelBytes, tm, 64, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
-        }
+        const CUtensorMap *tm = (i & 1) ? &tmap_v : &tmap_k;
+        mbar_expect_tx(&sh->kv_full[stage], kTileBytes);
+        tma_load_3d(dst, tm, 0, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
+        tma_load_3d(dst + kPanelBytes, tm, 64, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
       }
     }
   } else if (warp == 9) {

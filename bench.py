@@ -508,6 +508,31 @@ def run_suite(args):
     add("5-reshape_and_cache 4288 tokens", "hbm", 4288 * hkv * 128 * 2 * 2 * 2, r_ms, 0.0)
     del pw, buf, kc, vc, kk
 
+    # prefill from the paged cache (the "next" row): the same long-context problem with K/V living
+    # in cache blocks, against gather_cached_kv + packed prefill (what rLLM's call sequence does)
+    L = 8192
+    pw = workloads.prefill_long(dev, shard=shard, seqlen=L)
+    hkv = pw.k.shape[1]
+    nblk = 2 * L // 16 + 8
+    table, rows_ = workloads.build_block_tables([L, L], nblk, 4100)
+    slots = torch.tensor([r[t // 16] * 16 + t % 16 for r in rows_ for t in range(L)], dtype=torch.int32, device=dev)
+    kc = torch.zeros(nblk, hkv, 16, 16, 8, dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros(nblk, hkv, 128, 16, dtype=torch.bfloat16, device=dev)
+    tch_cuda.reshape_and_cache(pw.k, pw.v, kc, vc, slots)
+    table_d = table.to(dev)
+    cl = torch.tensor([L, L], dtype=torch.int32, device=dev)
+    kg, vg = torch.empty_like(pw.k), torch.empty_like(pw.v)
+
+    def gather_then_packed():
+        tch_cuda.gather_cached_kv(kg, vg, kc, vc, slots)
+        return tch_cuda.flash_attn_varlen(pw.q, kg, vg, pw.cu_seqlens_q, pw.cu_seqlens_k, L, L, pw.scale, True)
+    k_ms, _ = timed(gather_then_packed)
+    add("next: gather_cached_kv + packed prefill 2x%d" % L, "tensor", pw.flops(), k_ms, 0.0)
+    k_ms, _ = timed(lambda: tch_cuda.flash_attn_varlen_paged(pw.q, kc, vc, pw.cu_seqlens_q, cl, table_d, L, L,
+                                                             pw.scale, True))
+    add("next: paged prefill 2x%d (K/V read through block tables)" % L, "tensor", pw.flops(), k_ms, 0.0)
+    del pw, kc, vc, kg, vg
+
     # config 4: long prefill
     pw = workloads.prefill_long(dev, shard=shard)
     buf = torch.empty(world, *pw.q.shape, dtype=torch.bfloat16, device=dev)
