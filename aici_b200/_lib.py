@@ -16,6 +16,7 @@ EXPORTS = (
     "aici_last_status",
     "aici_reshape_and_cache",
     "aici_gather_cached_kv",
+    "aici_rotary_reshape_and_cache",
     "aici_copy_blocks",
     "aici_copy_blocks_host",
     "aici_paged_attention_workspace_bytes",

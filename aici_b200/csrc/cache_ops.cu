@@ -398,3 +398,187 @@ extern "C" char *aici_copy_blocks_host(const int64_t *key_cache_ptrs_host,
   }
   return nullptr;
 }
+
+// ---- rotary embedding fused with the cache write -----------------------------------------------------
+//
+// The step right before the attention path in rLLM is rotary_embedding on q and k
+// (rllm-cuda/src/llm/mod.rs:62-129 -> kernels/vllm/pos_encoding_kernels.cu:40-128), immediately
+// followed by reshape_and_cache of k and v.  This kernel does both in one pass over the tokens:
+// q and k are rotated in place (NeoX style, element i pairs with i + rot_dim/2, arithmetic in bf16
+// exactly as the reference's `x * cos - y * sin` on __nv_bfloat16) and the rotated k together with
+// v goes straight into the paged cache, so k is read once instead of three times.
+// One CTA = 16 tokens x one kv head (and the query heads of its group).
+namespace aici {
+
+__device__ __forceinline__ void rotate8(uint4 &xv, uint4 &yv, const uint4 &cv, const uint4 &sv) {
+  __nv_bfloat16 *x = reinterpret_cast<__nv_bfloat16 *>(&xv);
+  __nv_bfloat16 *y = reinterpret_cast<__nv_bfloat16 *>(&yv);
+  const __nv_bfloat16 *c = reinterpret_cast<const __nv_bfloat16 *>(&cv);
+  const __nv_bfloat16 *s = reinterpret_cast<const __nv_bfloat16 *>(&sv);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const __nv_bfloat16 xx = x[j], yy = y[j];
+    // every product and the sum is rounded to bf16 on its own, as the reference's 16-bit scalar
+    // type does (pos_encoding_kernels.cu:35-36); the _rn forms keep the compiler from fusing
+    // a product and the sum into one fma
+    x[j] = __hsub_rn(__hmul_rn(xx, c[j]), __hmul_rn(yy, s[j]));
+    y[j] = __hadd_rn(__hmul_rn(yy, c[j]), __hmul_rn(xx, s[j]));
+  }
+}
+
+template <bool kSlot64>
+__global__ void __launch_bounds__(kThreads)
+rotary_reshape_and_cache_kernel(const int64_t *__restrict__ positions, __nv_bfloat16 *__restrict__ query,
+                                __nv_bfloat16 *__restrict__ key, const __nv_bfloat16 *__restrict__ value,
+                                const __nv_bfloat16 *__restrict__ cos_sin_cache,
+                                __nv_bfloat16 *__restrict__ key_cache, __nv_bfloat16 *__restrict__ value_cache,
+                                const void *__restrict__ slot_mapping, int num_tokens, int num_kv_heads,
+                                int group, int64_t max_position, int64_t num_slots, int64_t query_stride,
+                                int64_t key_stride, int64_t value_stride, unsigned int *status) {
+  __shared__ int64_t s_slot[kTok];
+  __shared__ int64_t s_pos[kTok];
+  __shared__ __align__(16) __nv_bfloat16 s_v[kTok][kD + 8];
+  const int t0 = blockIdx.x * kTok;
+  const int h = blockIdx.y;
+  const int tid = threadIdx.x;
+
+  if (tid < kTok) {
+    int64_t slot = -1, pos = -1;
+    if (t0 + tid < num_tokens) {
+      slot = load_slot<kSlot64>(slot_mapping, t0 + tid);
+      if (slot >= num_slots) {
+        set_status(status, AICI_STATUS_BAD_SLOT);
+        slot = -1;
+      }
+      pos = positions[t0 + tid];
+      if (pos < 0 || pos >= max_position) {
+        set_status(status, AICI_STATUS_BAD_SLOT);
+        pos = -1;  // token left untouched
+      }
+    }
+    s_slot[tid] = slot;
+    s_pos[tid] = pos;
+  }
+  __syncthreads();
+
+  if (tid < 128) {
+    // thread (c, tok): d = 8c .. 8c+7 pairs with d + 64
+    const int c = tid >> 4, tok = tid & 15;
+    const int64_t pos = s_pos[tok];
+    if (t0 + tok < num_tokens && pos >= 0) {
+      const __nv_bfloat16 *cs = cos_sin_cache + pos * kD;  // [cos 0..63 | sin 0..63]
+      const uint4 cv = *reinterpret_cast<const uint4 *>(cs + c * kX);
+      const uint4 sv = *reinterpret_cast<const uint4 *>(cs + kD / 2 + c * kX);
+      // key head h
+      __nv_bfloat16 *kp = key + (int64_t)(t0 + tok) * key_stride + h * kD;
+      uint4 xv = *reinterpret_cast<const uint4 *>(kp + c * kX);
+      uint4 yv = *reinterpret_cast<const uint4 *>(kp + kD / 2 + c * kX);
+      rotate8(xv, yv, cv, sv);
+      *reinterpret_cast<uint4 *>(kp + c * kX) = xv;
+      *reinterpret_cast<uint4 *>(kp + kD / 2 + c * kX) = yv;
+      const int64_t slot = s_slot[tok];
+      if (slot >= 0) {
+        const int64_t blk = slot / kB, off = slot % kB;
+        __nv_bfloat16 *dst = key_cache + ((blk * num_kv_heads + h) * (kD / kX)) * (kB * kX) + off * kX;
+        *reinterpret_cast<uint4 *>(dst + c * (kB * kX)) = xv;
+        *reinterpret_cast<uint4 *>(dst + (c + 8) * (kB * kX)) = yv;
+      }
+      // the query heads of this kv head's group
+      for (int gq = 0; gq < group; ++gq) {
+        __nv_bfloat16 *qp = query + (int64_t)(t0 + tok) * query_stride + (h * group + gq) * kD;
+        uint4 qx = *reinterpret_cast<const uint4 *>(qp + c * kX);
+        uint4 qy = *reinterpret_cast<const uint4 *>(qp + kD / 2 + c * kX);
+        rotate8(qx, qy, cv, sv);
+        *reinterpret_cast<uint4 *>(qp + c * kX) = qx;
+        *reinterpret_cast<uint4 *>(qp + kD / 2 + c * kX) = qy;
+      }
+    }
+  } else {
+    // value tile -> shared memory (two 16-byte pieces per thread), transposed out below
+    const int i = tid - 128;
+    const int tok = i >> 3, part = (i & 7) * 2;
+    if (s_slot[tok] >= 0) {
+      const __nv_bfloat16 *vp = value + (int64_t)(t0 + tok) * value_stride + h * kD;
+      *reinterpret_cast<uint4 *>(&s_v[tok][part * kX]) = *reinterpret_cast<const uint4 *>(vp + part * kX);
+      *reinterpret_cast<uint4 *>(&s_v[tok][(part + 1) * kX]) = *reinterpret_cast<const uint4 *>(vp + (part + 1) * kX);
+    }
+  }
+  __syncthreads();
+  {
+    const int d = tid & (kD - 1), half = tid >> 7;
+    const int tb = half * 8;
+    const int64_t s0 = s_slot[tb];
+    bool run = s0 >= 0 && (s0 % 8) == 0;
+#pragma unroll
+    for (int j = 1; j < 8; ++j) run = run && (s_slot[tb + j] == s0 + j);
+    if (run) {
+      uint4 val;
+      __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&val);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = s_v[tb + j][d];
+      const int64_t blk = s0 / kB, off = s0 % kB;
+      *reinterpret_cast<uint4 *>(value_cache + ((blk * num_kv_heads + h) * kD + d) * kB + off) = val;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int64_t slot = s_slot[tb + j];
+        if (slot >= 0) {
+          const int64_t blk = slot / kB, off = slot % kB;
+          value_cache[((blk * num_kv_heads + h) * kD + d) * kB + off] = s_v[tb + j][d];
+        }
+      }
+    }
+  }
+}
+
+}  // namespace aici
+
+extern "C" char *aici_rotary_reshape_and_cache(const int64_t *positions, void *query, void *key,
+                                               const void *value, const void *cos_sin_cache,
+                                               void *key_cache, void *value_cache,
+                                               const void *slot_mapping, int slot_is_int64,
+                                               int num_tokens, int num_heads, int num_kv_heads,
+                                               int head_size, int rot_dim, int is_neox,
+                                               int64_t max_position, int block_size, int64_t num_blocks,
+                                               int64_t query_stride, int64_t key_stride,
+                                               int64_t value_stride, int dtype, aici_stream_t stream) {
+  const char *fn = "aici_rotary_reshape_and_cache";
+  if (char *e = check_cache_shape(fn, num_kv_heads, head_size, block_size, dtype)) return e;
+  AICI_CHECK(is_neox, "%s: only the NeoX pairing is supported (the reference's CPU path has no other)", fn);
+  AICI_CHECK(rot_dim == head_size, "%s: rot_dim must equal head_size (got %d)", fn, rot_dim);
+  AICI_CHECK(num_heads > 0 && num_heads % num_kv_heads == 0, "%s: num_heads must be a multiple of num_kv_heads", fn);
+  AICI_CHECK(num_tokens >= 0 && max_position > 0, "%s: bad sizes", fn);
+  if (num_tokens == 0) return nullptr;
+  AICI_CHECK(positions && query && key && value && cos_sin_cache && key_cache && value_cache && slot_mapping,
+             "%s: NULL pointer", fn);
+  AICI_CHECK(num_blocks > 0, "%s: num_blocks must be positive", fn);
+  AICI_CHECK(query_stride % 8 == 0 && key_stride % 8 == 0 && value_stride % 8 == 0 &&
+                 query_stride >= (int64_t)num_heads * head_size &&
+                 key_stride >= (int64_t)num_kv_heads * head_size &&
+                 value_stride >= (int64_t)num_kv_heads * head_size,
+             "%s: token strides must be multiples of 8 elements and cover one row", fn);
+  AICI_CHECK(((uintptr_t)query | (uintptr_t)key | (uintptr_t)value | (uintptr_t)cos_sin_cache |
+              (uintptr_t)key_cache | (uintptr_t)value_cache) % 16 == 0,
+             "%s: tensors must be 16-byte aligned", fn);
+  unsigned int *st = status_ptr();
+  AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
+  dim3 grid((num_tokens + kTok - 1) / kTok, num_kv_heads);
+  const int group = num_heads / num_kv_heads;
+  auto q = static_cast<__nv_bfloat16 *>(query);
+  auto k = static_cast<__nv_bfloat16 *>(key);
+  auto v = static_cast<const __nv_bfloat16 *>(value);
+  auto cs = static_cast<const __nv_bfloat16 *>(cos_sin_cache);
+  auto kc = static_cast<__nv_bfloat16 *>(key_cache);
+  auto vc = static_cast<__nv_bfloat16 *>(value_cache);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (slot_is_int64)
+    rotary_reshape_and_cache_kernel<true><<<grid, kThreads, 0, s>>>(
+        positions, q, k, v, cs, kc, vc, slot_mapping, num_tokens, num_kv_heads, group, max_position,
+        num_blocks * kB, query_stride, key_stride, value_stride, st);
+  else
+    rotary_reshape_and_cache_kernel<false><<<grid, kThreads, 0, s>>>(
+        positions, q, k, v, cs, kc, vc, slot_mapping, num_tokens, num_kv_heads, group, max_position,
+        num_blocks * kB, query_stride, key_stride, value_stride, st);
+  AICI_CUDA(cudaGetLastError());
+  return nullptr;
+}

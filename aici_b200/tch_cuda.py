@@ -405,3 +405,40 @@ def flash_attn_varlen_paged(q: torch.Tensor, key_cache: torch.Tensor, value_cach
             ctypes.c_int(_dtype(fn, q)), _stream(dev))
     _lib.check(fn, res)
     return out
+
+
+def rotary_embedding_reshape_and_cache(positions: torch.Tensor, query: torch.Tensor, key: torch.Tensor,
+                                       value: torch.Tensor, head_size: int, cos_sin_cache: torch.Tensor,
+                                       is_neox: bool, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                                       slot_mapping: torch.Tensor) -> None:
+    """rotary_embedding (lib.rs:333-354) and reshape_and_cache (lib.rs:192-213) in one pass:
+    `query` [num_tokens, num_heads * head_size] and `key` [num_tokens, num_kv_heads * head_size]
+    are rotated in place and the rotated key plus `value` go into the paged cache."""
+    fn = "rotary_embedding_reshape_and_cache"
+    dev = _require_cuda(fn, positions, query, key, value, cos_sin_cache, key_cache, value_cache, slot_mapping)
+    num_blocks, num_kv_heads, cache_head, block_size = _cache_dims(fn, key_cache, value_cache)
+    if cache_head != head_size:
+        raise AiciError("%s: head_size does not match the cache" % fn)
+    T = query.shape[0]
+    q2, k2, v2 = query.view(T, -1), key.view(T, -1), value.view(T, -1)
+    if q2.stride(1) != 1 or k2.stride(1) != 1 or v2.stride(1) != 1:
+        raise AiciError("%s: rows must be contiguous" % fn)
+    if k2.shape[1] != num_kv_heads * head_size or v2.shape[1] != k2.shape[1] or q2.shape[1] % head_size:
+        raise AiciError("%s: key/value width does not match the cache" % fn)
+    if positions.dtype != torch.int64 or not positions.is_contiguous() or positions.numel() != T:
+        raise AiciError("%s: positions must be contiguous int64 [num_tokens]" % fn)
+    if slot_mapping.dtype not in (torch.int32, torch.int64) or not slot_mapping.is_contiguous() or \
+            slot_mapping.numel() != T:
+        raise AiciError("%s: slot_mapping must be contiguous int32 or int64 [num_tokens]" % fn)
+    if cos_sin_cache.dim() != 2 or not cos_sin_cache.is_contiguous() or cos_sin_cache.dtype != query.dtype:
+        raise AiciError("%s: cos_sin_cache must be contiguous [max_position, rot_dim] of the query dtype" % fn)
+    with torch.cuda.device(dev):
+        res = _lib.lib().aici_rotary_reshape_and_cache(
+            _p(positions), _p(query), _p(key), _p(value), _p(cos_sin_cache), _p(key_cache), _p(value_cache),
+            _p(slot_mapping), ctypes.c_int(1 if slot_mapping.dtype == torch.int64 else 0), ctypes.c_int(T),
+            ctypes.c_int(q2.shape[1] // head_size), ctypes.c_int(num_kv_heads), ctypes.c_int(head_size),
+            ctypes.c_int(cos_sin_cache.shape[1]), ctypes.c_int(1 if is_neox else 0),
+            ctypes.c_int64(cos_sin_cache.shape[0]), ctypes.c_int(block_size), ctypes.c_int64(num_blocks),
+            ctypes.c_int64(q2.stride(0)), ctypes.c_int64(k2.stride(0)), ctypes.c_int64(v2.stride(0)),
+            ctypes.c_int(_dtype(fn, query)), _stream(dev))
+    _lib.check(fn, res)

@@ -85,6 +85,21 @@ char *aici_copy_blocks_host(const int64_t *key_cache_ptrs_host,
                             int64_t numel_per_block, int64_t num_blocks, int dtype,
                             aici_stream_t stream);
 
+/* Rotary embedding fused with the cache write: rotary_embedding_C (lib.rs:139-146;
+ * kernels/vllm/pos_encoding_kernels.cu:40-128) followed by reshape_and_cache_C, as rLLM issues
+ * them back to back (rllm-cuda/src/llm/mod.rs:107-114, 158-164), in one pass.  query
+ * [num_tokens, num_heads, head_size] and key [num_tokens, num_kv_heads, head_size] are rotated in
+ * place (NeoX pairing, bf16 arithmetic as in the reference kernel); the rotated key and `value` are
+ * written to the paged cache at slot_mapping.  positions int64 [num_tokens]; cos_sin_cache
+ * [max_position, rot_dim] = [cos | sin].  Requires rot_dim == head_size == 128 and is_neox != 0. */
+char *aici_rotary_reshape_and_cache(const int64_t *positions, void *query, void *key,
+                                    const void *value, const void *cos_sin_cache, void *key_cache,
+                                    void *value_cache, const void *slot_mapping, int slot_is_int64,
+                                    int num_tokens, int num_heads, int num_kv_heads, int head_size,
+                                    int rot_dim, int is_neox, int64_t max_position, int block_size,
+                                    int64_t num_blocks, int64_t query_stride, int64_t key_stride,
+                                    int64_t value_stride, int dtype, aici_stream_t stream);
+
 /* ---- decode attention over the paged cache ----------------------------------------- */
 
 /* Bytes of caller-owned scratch aici_paged_attention_v1 needs for these sizes (the chunk size of

@@ -1,5 +1,5 @@
 """Builds oracle/_ref/libref_vllm.so: the reference's OWN paged-attention and KV-cache CUDA
-kernels, compiled unmodified for sm_100a from where they lie in the reference tree, plus a small
+kernels (and rotary embedding), compiled unmodified for sm_100a from where they lie in the reference tree, plus a small
 plain-pointer shim (oracle/ref_shim.cpp).  TEST INFRASTRUCTURE: a GPU-side comparator for the
 parity tests, never part of the product.
 
@@ -25,6 +25,7 @@ def build(force: bool = False):
     ref = os.environ.get("AICI_REFERENCE_DIR", "/root/reference")
     kdir = os.path.join(ref, "rllm", "tch-cuda", "kernels")
     srcs = [os.path.join(kdir, "vllm", "cache_kernels.cu"),
+            os.path.join(kdir, "vllm", "pos_encoding_kernels.cu"),
             os.path.join(kdir, "vllm", "attention", "attention_kernels.cu")]
     if not all(os.path.exists(s) for s in srcs):
         return None

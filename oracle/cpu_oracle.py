@@ -162,6 +162,20 @@ def flash_attn_varlen_rows(q, k, v, seqlens_q, seqlens_k, rows, softmax_scale, c
     return out
 
 
+def rotary_embedding(positions, query, key, head_size, cos_sin_cache, is_neox=True):
+    """In place on query [T, Hq*D] / key [T, Hkv*D] (or 3-D). pos_encoding_kernels.cu:9-128."""
+    assert is_neox, "the reference's CPU path implements only the NeoX pairing (refkernels.rs:170-185)"
+    T = query.shape[0]
+    q2, k2 = query.view(T, -1), key.view(T, -1)
+    assert q2.stride(1) == 1 and k2.stride(1) == 1
+    pos = positions.to(torch.int64).contiguous()
+    cs = cos_sin_cache.contiguous()
+    lib().oracle_rotary_embedding_neox(
+        _ptr(pos), _u16(query), _u16(key), _u16(cs), ctypes.c_int(T), ctypes.c_int(q2.shape[1] // head_size),
+        ctypes.c_int(k2.shape[1] // head_size), ctypes.c_int(head_size), ctypes.c_int(cs.shape[1]),
+        ctypes.c_int64(q2.stride(0)), ctypes.c_int64(k2.stride(0)))
+
+
 def round_to_bf16(x: torch.Tensor) -> torch.Tensor:
     x = x.contiguous().to(torch.float32)
     out = torch.empty(x.shape, dtype=torch.bfloat16)

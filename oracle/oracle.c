@@ -369,6 +369,32 @@ void oracle_varlen_attn_rows(float *out_f32, const uint16_t *q, const uint16_t *
   }
 }
 
+/* rotary_embedding, NeoX pairing: rllm/tch-cuda/kernels/vllm/pos_encoding_kernels.cu:9-80.
+ * query [T, Hq, D] and key [T, Hkv, D] rotated in place; cos_sin_cache [max_position, rot_dim]
+ * = [cos 0..rot/2 | sin 0..rot/2].  The kernel computes `x*cos - y*sin` and `y*cos + x*sin` on the
+ * 16-bit scalar type: every product and the sum/difference is rounded to bf16. */
+void oracle_rotary_embedding_neox(const int64_t *positions, uint16_t *query, uint16_t *key,
+                                  const uint16_t *cos_sin_cache, int num_tokens, int num_heads,
+                                  int num_kv_heads, int head_size, int rot_dim, int64_t query_stride,
+                                  int64_t key_stride) {
+  const int embed = rot_dim / 2;
+  for (int64_t t = 0; t < num_tokens; ++t) {
+    const uint16_t *cs = cos_sin_cache + positions[t] * rot_dim;
+    for (int pass = 0; pass < 2; ++pass) {
+      uint16_t *base = pass == 0 ? query + t * query_stride : key + t * key_stride;
+      const int heads = pass == 0 ? num_heads : num_kv_heads;
+      for (int h = 0; h < heads; ++h)
+        for (int i = 0; i < embed; ++i) {
+          uint16_t *arr = base + (int64_t)h * head_size;
+          const float c = bf16_to_f32(cs[i]), s = bf16_to_f32(cs[embed + i]);
+          const float x = bf16_to_f32(arr[i]), y = bf16_to_f32(arr[embed + i]);
+          arr[i] = f32_to_bf16(round_bf16(x * c) - round_bf16(y * s));
+          arr[embed + i] = f32_to_bf16(round_bf16(y * c) + round_bf16(x * s));
+        }
+    }
+  }
+}
+
 /* bf16 round-trip helper exposed so Python can round an fp32 buffer exactly as the GPU
  * store does (round-to-nearest-even). */
 void oracle_round_to_bf16(const float *in, uint16_t *out, int64_t n) {

@@ -65,6 +65,17 @@ char *ref_copy_blocks_2(void *kptrs, void *vptrs, void *mapping, int64_t layers,
   })
 }
 
+char *ref_rotary_embedding(void *positions_i64, void *query, void *key, int64_t T, int64_t hq, int64_t hkv,
+                           int64_t d, void *cos_sin, int64_t max_pos, int64_t rot_dim, int is_neox, int dev) {
+  REF_PROTECT({
+    auto pos = wrap(positions_i64, {T}, torch::kInt64, dev);
+    auto q = wrap(query, {T, hq * d}, torch::kBFloat16, dev);
+    auto k = wrap(key, {T, hkv * d}, torch::kBFloat16, dev);
+    auto cs = wrap(cos_sin, {max_pos, rot_dim}, torch::kBFloat16, dev);
+    rotary_embedding(pos, q, k, (int)d, cs, is_neox != 0);
+  })
+}
+
 char *ref_paged_attention_v1(void *out, void *query, void *kc, void *vc, int num_kv_heads, float scale,
                              void *block_tables, void *context_lens, int block_size,
                              int max_context_len, int64_t S, int64_t hq, int64_t d, int64_t max_blocks,

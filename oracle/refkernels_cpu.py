@@ -62,6 +62,38 @@ def repeat_kv(x, n_rep):
     return x if n_rep == 1 else x.repeat_interleave(n_rep, dim=1)
 
 
+def rotary_embedding(positions, query0, key0, head_size, cos_sin_cache, is_neox=True):
+    """refkernels.rs:150-211, NeoX only (the other branch is todo!() there).  In place."""
+    assert is_neox
+    rot_dim = cos_sin_cache.shape[1]
+    num_tokens = query0.shape[0]
+    query = query0.view(num_tokens, -1, head_size)
+    key = key0.view(num_tokens, -1, head_size)
+    cos, sin = cos_sin_cache[positions.long()].chunk(2, -1)
+    cos = cos.repeat(1, 2).unsqueeze(-2)
+    sin = sin.repeat(1, 2).unsqueeze(-2)
+
+    def rotate(x):
+        off = x.shape[2] // 2
+        return torch.cat([-x[:, :, off:], x[:, :, :off]], -1)
+
+    q_rot, k_rot = query[:, :, :rot_dim], key[:, :, :rot_dim]
+    q_new = q_rot * cos + rotate(q_rot) * sin
+    k_new = k_rot * cos + rotate(k_rot) * sin
+    if head_size > rot_dim:
+        q_new = torch.cat([q_new, query[:, :, rot_dim:]], -1)
+        k_new = torch.cat([k_new, key[:, :, rot_dim:]], -1)
+    query0.copy_(q_new.reshape(query0.shape))
+    key0.copy_(k_new.reshape(key0.shape))
+
+
+def make_cos_sin_cache(max_position, rot_dim, theta=10000.0, dtype=torch.bfloat16):
+    """RotaryEmbedding::new, rllm-cuda/src/llm/mod.rs:41-60."""
+    inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float32) / rot_dim))
+    idx = torch.arange(max_position, dtype=torch.float32).reshape(-1, 1) @ inv.reshape(1, -1)
+    return torch.cat([idx.cos().to(dtype), idx.sin().to(dtype)], -1).contiguous()
+
+
 def decode_step_cpu(query, key_cache, value_cache, num_kv_heads, scale, block_tables,
                     context_lens, block_size):
     """What rLLM's CPU build does for single-token sequences: there is no paged kernel

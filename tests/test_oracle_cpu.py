@@ -183,3 +183,25 @@ def test_varlen_oracle_vs_refkernels_port(lens_q, lens_k):
     rows = torch.tensor([[0, 0, 0], [len(lens_q) - 1, sum(lens_q) - 1, hq - 1]], dtype=torch.int32)
     r = O.flash_attn_varlen_rows(q, k, v, cq, ck, rows, scale, True)
     assert torch.allclose(r[0], a[0, 0]) and torch.allclose(r[1], a[-1, hq - 1])
+
+
+def test_rotary_oracle_vs_refkernels_port():
+    g = torch.Generator().manual_seed(21)
+    T, hq, hkv, d = 11, 4, 2, 128
+    cs = R.make_cos_sin_cache(300, d)
+    pos = torch.randint(0, 300, (T,), generator=g)
+    q = torch.randn(T, hq * d, generator=g).to(torch.bfloat16)
+    k = torch.randn(T, hkv * d, generator=g).to(torch.bfloat16)
+    q1, k1 = q.clone(), k.clone()
+    O.rotary_embedding(pos, q1, k1, d, cs)
+    q2, k2 = q.float(), k.float()
+    R.rotary_embedding(pos, q2, k2, d, cs.float())
+    # the kernel rounds both products and the sum to bf16 (inputs are ~N(0,1), |x| < 5): each
+    # rounding is at most half an ulp of a value below 8, i.e. 2^-6
+    for a, b in ((q1, q2), (k1, k2)):
+        diff = (a.float() - b).abs()
+        assert float(diff.max()) <= 3 * 2.0 ** -6 and float(diff.mean()) <= 5e-3
+    # position 0 is the identity (cos 1, sin 0)
+    q3, k3 = q.clone(), k.clone()
+    O.rotary_embedding(torch.zeros(T, dtype=torch.int64), q3, k3, d, cs)
+    assert torch.equal(q3, q) and torch.equal(k3, k)
