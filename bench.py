@@ -41,7 +41,7 @@ CPU_SAMPLE_SEQS = 8
 # DRAM bytes (read + write) of paged_decode_kernel per algorithmic byte, from the ncu capture of
 # the 16-sequence case summarised in profiles/paged_decode_kernel_llama2_7b_16seq.md; traffic
 # grows in proportion to the tokens read, so the ratio carries over to the full launch.
-DECODE_TRAFFIC_RATIO = 1.016
+DECODE_TRAFFIC_RATIO = 1.025
 
 
 def load_peaks():
@@ -359,7 +359,7 @@ def run_ours(args):
                 "d2h_bytes_per_step": d2h,
                 "note": "q, new k/v, slot map, block tables, context lens copied from pinned host memory "
                         "and the output read back every step; the KV cache is resident state"},
-        "gpu_launches": 4 * args.steps,
+        "gpu_launches": 3 * args.steps,  # reshape_and_cache, paged_decode, paged_merge per step
         "clocks": clocks,
         "prefill": {
             "workload": pw.name + "_causal_d128", "tflops": p_tflops, "ms_per_step": p_ms, "steps": p_steps,
