@@ -19,6 +19,7 @@ EXPORTS = (
     "aici_rotary_reshape_and_cache",
     "aici_copy_blocks",
     "aici_copy_blocks_host",
+    "aici_tune_decode_chunk",
     "aici_paged_attention_workspace_bytes",
     "aici_paged_attention_v1",
     "aici_paged_attention_v2",
@@ -49,7 +50,6 @@ def lib() -> ctypes.CDLL:
             fn = getattr(_lib, name)
             if name not in ("aici_version", "aici_paged_attention_workspace_bytes"):
                 fn.restype = ctypes.c_void_p  # char*, released with free()
-        _lib.aici_tune_decode_chunk.restype = ctypes.c_void_p
         _libc = ctypes.CDLL(None)
         _libc.free.argtypes = [ctypes.c_void_p]
         _lib._free = _libc.free

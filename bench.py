@@ -38,9 +38,9 @@ METRIC = "paged-decode attn HBM TB/s (prefill attn TFLOPS under 'prefill')"
 UNIT = "TB/s"
 WORKLOAD = "decode_llama2_7b_b64_mha32_d128_bs16_ctx512-4096_pool16384+reshape_and_cache_64"
 CPU_SAMPLE_SEQS = 8
-# DRAM bytes (read + write) of paged_decode_kernel per algorithmic byte, from the ncu capture of
-# the 16-sequence case summarised in profiles/paged_decode_kernel_llama2_7b_16seq.md; traffic
-# grows in proportion to the tokens read, so the ratio carries over to the full launch.
+# DRAM bytes (read + write) of paged_decode_kernel per algorithmic byte, from an ncu capture of
+# the 16-sequence case that `--profile decode` runs; traffic grows in proportion to the tokens
+# read, so the ratio carries over to the full launch.
 DECODE_TRAFFIC_RATIO = 1.025
 
 
@@ -353,7 +353,7 @@ def run_ours(args):
             "frac": achieved_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
             "launch_ms": att_ms,
             "traffic": DECODE_TRAFFIC_RATIO * decode_bytes_local,
-            "traffic_note": "ncu dram read+write of a 16-sequence launch scaled by bytes (profiles/)",
+            "traffic_note": "ncu dram read+write of a 16-sequence launch, scaled by bytes",
         },
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h,

@@ -102,6 +102,11 @@ char *aici_rotary_reshape_and_cache(const int64_t *positions, void *query, void 
 
 /* ---- decode attention over the paged cache ----------------------------------------- */
 
+/* Tuning hook for benchmarks: tokens per chunk of the context split used by
+ * aici_paged_attention_v1 (a multiple of 16 up to 512); 0 restores the batch-adaptive default.
+ * Process-wide; changes what aici_paged_attention_workspace_bytes returns. */
+char *aici_tune_decode_chunk(int chunk_tokens);
+
 /* Bytes of caller-owned scratch aici_paged_attention_v1 needs for these sizes (the chunk size of
  * the context split, and with it the number of partial results, depends on all four). */
 size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads, int num_kv_heads,

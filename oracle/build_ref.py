@@ -5,7 +5,8 @@ parity tests, never part of the product.
 
     python oracle/build_ref.py [--force]
 
-Needs the reference checkout (default /root/reference, override with AICI_REFERENCE_DIR) and the
+Needs the reference checkout (the directory named by AICI_REFERENCE_DIR, default `reference` next to
+the repository's parent) and the
 installed PyTorch headers/libraries (the kernels are written against libtorch).  Takes about ten
 minutes.  Where the reference tree is absent the script does nothing; the prebuilt library in
 oracle/_ref/ (git-ignored) is what travels to a GPU machine.  The reference's flash-attention
@@ -22,7 +23,8 @@ OUT = os.path.join(OUT_DIR, "libref_vllm.so")
 
 
 def build(force: bool = False):
-    ref = os.environ.get("AICI_REFERENCE_DIR", "/root/reference")
+    ref = os.environ.get("AICI_REFERENCE_DIR",
+                         os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
     kdir = os.path.join(ref, "rllm", "tch-cuda", "kernels")
     srcs = [os.path.join(kdir, "vllm", "cache_kernels.cu"),
             os.path.join(kdir, "vllm", "pos_encoding_kernels.cu"),
