@@ -37,7 +37,10 @@ struct DecodeParams {
   const __nv_bfloat16 *q;
   const __nv_bfloat16 *k_cache;
   const __nv_bfloat16 *v_cache;
-  __nv_bfloat16 *out;
+  // output rows [num_seqs, out_heads, 128] in `world` buffers (this GPU's and, for the fused
+  // gather, every peer's): this rank's heads start at out_head0
+  __nv_bfloat16 *out[8];
+  int world, out_heads, out_head0;
   const int32_t *block_tables;
   const int32_t *context_lens;
   const int2 *entries;   // compacted (seq, chunk) list, or NULL: every (seq, chunk < max_parts)
@@ -328,10 +331,13 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
       const float inv = __fdividef(1.f, l_run + 1e-6f);
       const int n_chunks = (it.ctx + p.chunk_tokens - 1) / p.chunk_tokens;
       if (n_chunks == 1) {
-        __nv_bfloat16 *dst = p.out + ((int64_t)it.seq * p.num_heads + head) * kD + 2 * tig;
+        const int64_t off = ((int64_t)it.seq * p.out_heads + p.out_head0 + head) * kD + 2 * tig;
+        for (int w = 0; w < p.world; ++w) {
+          __nv_bfloat16 *dst = p.out[w] + off;
 #pragma unroll
-        for (int nt = 0; nt < 16; ++nt)
-          store_pair<__nv_bfloat16>(dst + 8 * nt, o[nt][0] * inv, o[nt][1] * inv);
+          for (int nt = 0; nt < 16; ++nt)
+            store_pair<__nv_bfloat16>(dst + 8 * nt, o[nt][0] * inv, o[nt][1] * inv);
+        }
       }
       if (n_chunks > 1 || p.always_write_partials) {
         const int64_t pidx = ((int64_t)it.seq * p.num_heads + head) * p.max_parts + it.chunk;
@@ -369,9 +375,10 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const Dec
   const int ctx = clamp_ctx(p, p.context_lens[seq]);
   const int n = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
   if (n == 1) return;  // the decode kernel wrote the row itself
-  uint2 *dst = reinterpret_cast<uint2 *>(p.out + ((int64_t)seq * p.num_heads + head) * kD + 4 * lane);
+  const int64_t out_off = ((int64_t)seq * p.out_heads + p.out_head0 + head) * kD + 4 * lane;
   if (n <= 0) {
-    if (warp == 0) *dst = make_uint2(0u, 0u);
+    if (warp == 0)
+      for (int w = 0; w < p.world; ++w) *reinterpret_cast<uint2 *>(p.out[w] + out_off) = make_uint2(0u, 0u);
     return;
   }
   const int64_t base = ((int64_t)seq * p.num_heads + head) * p.max_parts;
@@ -418,7 +425,8 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const Dec
       tw += s_w[w];
     }
     const float inv = __fdividef(1.f, tw + 1e-6f);
-    *dst = make_uint2(pack_bf16(t0 * inv, t1 * inv), pack_bf16(t2 * inv, t3 * inv));
+    const uint2 row = make_uint2(pack_bf16(t0 * inv, t1 * inv), pack_bf16(t2 * inv, t3 * inv));
+    for (int w = 0; w < p.world; ++w) *reinterpret_cast<uint2 *>(p.out[w] + out_off) = row;
   }
 }
 
@@ -620,17 +628,19 @@ extern "C" size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_hea
                           pick_chunk(num_seqs, num_kv_heads, max_context_len)).total;
 }
 
-extern "C" char *aici_paged_attention_v1(void *out, const void *query, const void *key_cache,
-                                         const void *value_cache, int num_kv_heads, float scale,
-                                         const int32_t *block_tables, const int32_t *context_lens,
-                                         int block_size, int max_context_len,
-                                         const float *alibi_slopes, int num_seqs, int num_heads,
-                                         int head_size, int max_num_blocks_per_seq,
-                                         int64_t num_blocks, int64_t q_stride,
-                                         int64_t kv_block_stride, int64_t kv_head_stride,
-                                         void *workspace, size_t workspace_bytes, int dtype,
-                                         aici_stream_t stream) {
-  const char *fn = "aici_paged_attention_v1";
+static char *paged_attention_v1_impl(const char *fn, void *const *outs, int world, int out_heads,
+                                     int out_head0, const void *query, const void *key_cache,
+                                     const void *value_cache, int num_kv_heads, float scale,
+                                     const int32_t *block_tables, const int32_t *context_lens,
+                                     int block_size, int max_context_len, const float *alibi_slopes,
+                                     int num_seqs, int num_heads, int head_size,
+                                     int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_stride,
+                                     int64_t kv_block_stride, int64_t kv_head_stride, void *workspace,
+                                     size_t workspace_bytes, int dtype, aici_stream_t stream) {
+  void *out = outs[0];
+  for (int w = 1; w < world; ++w)
+    AICI_CHECK(outs[w] != nullptr && (uintptr_t)outs[w] % 16 == 0,
+               "%s: peer output %d must be non-NULL and 16-byte aligned", fn, w);
   if (char *e = check_decode_args(fn, out, query, key_cache, value_cache, num_kv_heads,
                                   block_tables, context_lens, block_size, max_context_len,
                                   alibi_slopes, num_seqs, num_heads, head_size,
@@ -650,7 +660,10 @@ extern "C" char *aici_paged_attention_v1(void *out, const void *query, const voi
   p.q = static_cast<const __nv_bfloat16 *>(query);
   p.k_cache = static_cast<const __nv_bfloat16 *>(key_cache);
   p.v_cache = static_cast<const __nv_bfloat16 *>(value_cache);
-  p.out = static_cast<__nv_bfloat16 *>(out);
+  for (int i = 0; i < 8; ++i) p.out[i] = static_cast<__nv_bfloat16 *>(i < world ? outs[i] : nullptr);
+  p.world = world;
+  p.out_heads = out_heads;
+  p.out_head0 = out_head0;
   p.block_tables = block_tables;
   p.context_lens = context_lens;
   p.part_max = reinterpret_cast<float *>(ws + w.max_off);
@@ -674,6 +687,50 @@ extern "C" char *aici_paged_attention_v1(void *out, const void *query, const voi
   return launch_decode<float>(p, reinterpret_cast<int2 *>(ws + w.entries_off),
                               reinterpret_cast<int *>(ws + w.n_entries_off),
                               static_cast<cudaStream_t>(stream));
+}
+
+extern "C" char *aici_paged_attention_v1(void *out, const void *query, const void *key_cache,
+                                         const void *value_cache, int num_kv_heads, float scale,
+                                         const int32_t *block_tables, const int32_t *context_lens,
+                                         int block_size, int max_context_len,
+                                         const float *alibi_slopes, int num_seqs, int num_heads,
+                                         int head_size, int max_num_blocks_per_seq,
+                                         int64_t num_blocks, int64_t q_stride,
+                                         int64_t kv_block_stride, int64_t kv_head_stride,
+                                         void *workspace, size_t workspace_bytes, int dtype,
+                                         aici_stream_t stream) {
+  void *outs[1] = {out};
+  return paged_attention_v1_impl("aici_paged_attention_v1", outs, 1, num_heads, 0, query, key_cache,
+                                 value_cache, num_kv_heads, scale, block_tables, context_lens, block_size,
+                                 max_context_len, alibi_slopes, num_seqs, num_heads, head_size,
+                                 max_num_blocks_per_seq, num_blocks, q_stride, kv_block_stride,
+                                 kv_head_stride, workspace, workspace_bytes, dtype, stream);
+}
+
+// Decode attention whose epilogue is the head-output gather: every finished output row is stored
+// to its final place [seq, head0 + head, :] in the output buffer of EVERY rank (plain stores to
+// peer-mapped memory over NVLink), so no collective runs afterwards; the ranks only need a
+// barrier before reading.  outs[] lists the world's buffers (this rank's own included), each
+// [num_seqs, total_heads, 128].
+extern "C" char *aici_paged_attention_v1_peers(void *const *outs, int world, int total_heads, int head0,
+                                               const void *query, const void *key_cache,
+                                               const void *value_cache, int num_kv_heads, float scale,
+                                               const int32_t *block_tables, const int32_t *context_lens,
+                                               int block_size, int max_context_len, int num_seqs,
+                                               int num_heads, int head_size, int max_num_blocks_per_seq,
+                                               int64_t num_blocks, int64_t q_stride,
+                                               int64_t kv_block_stride, int64_t kv_head_stride,
+                                               void *workspace, size_t workspace_bytes, int dtype,
+                                               aici_stream_t stream) {
+  const char *fn = "aici_paged_attention_v1_peers";
+  AICI_CHECK(outs != nullptr && world >= 1 && world <= 8, "%s: world must be 1..8", fn);
+  AICI_CHECK(head0 >= 0 && num_heads > 0 && head0 + num_heads <= total_heads,
+             "%s: heads [%d, %d) do not fit %d total heads", fn, head0, head0 + num_heads, total_heads);
+  return paged_attention_v1_impl(fn, outs, world, total_heads, head0, query, key_cache, value_cache,
+                                 num_kv_heads, scale, block_tables, context_lens, block_size,
+                                 max_context_len, nullptr, num_seqs, num_heads, head_size,
+                                 max_num_blocks_per_seq, num_blocks, q_stride, kv_block_stride,
+                                 kv_head_stride, workspace, workspace_bytes, dtype, stream);
 }
 
 extern "C" char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_logits,
@@ -702,7 +759,10 @@ extern "C" char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_
   p.q = static_cast<const __nv_bfloat16 *>(query);
   p.k_cache = static_cast<const __nv_bfloat16 *>(key_cache);
   p.v_cache = static_cast<const __nv_bfloat16 *>(value_cache);
-  p.out = static_cast<__nv_bfloat16 *>(out);
+  for (int i = 0; i < 8; ++i) p.out[i] = i == 0 ? static_cast<__nv_bfloat16 *>(out) : nullptr;
+  p.world = 1;
+  p.out_heads = num_heads;
+  p.out_head0 = 0;
   p.block_tables = block_tables;
   p.context_lens = context_lens;
   p.part_max = max_logits;

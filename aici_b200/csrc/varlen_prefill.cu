@@ -38,7 +38,10 @@ constexpr float kRescaleThreshold = 8.f;  // log2 units: the running reference m
 constexpr float kDangerThreshold = 60.f;  // beyond this a tile is redone against its exact maximum (no overflow risk)
 
 struct PrefillParams {
-  __nv_bfloat16 *out;
+  // output [total_q, heads, 128] (strides below) in `world` buffers -- this GPU's and, for the
+  // fused head gather, every peer's; this rank's head h is written at head index out_head0 + h
+  __nv_bfloat16 *out[8];
+  int world, out_head0;
   const int32_t *cu_q;
   const int32_t *cu_k;
   int64_t o_tok_stride, o_head_stride;
@@ -73,8 +76,9 @@ __device__ __forceinline__ void zero_rows(const PrefillParams &p, int q0, const 
                                           int nthreads) {
   for (int i = tid; i < T.rows * (kHD / 8); i += nthreads) {
     const int r = i / (kHD / 8), c = i % (kHD / 8);
-    *reinterpret_cast<uint4 *>(p.out + (int64_t)(q0 + T.m0 + r) * p.o_tok_stride +
-                               (int64_t)T.h * p.o_head_stride + c * 8) = make_uint4(0, 0, 0, 0);
+    for (int w = 0; w < p.world; ++w)
+      *reinterpret_cast<uint4 *>(p.out[w] + (int64_t)(q0 + T.m0 + r) * p.o_tok_stride +
+                                 (int64_t)(p.out_head0 + T.h) * p.o_head_stride + c * 8) = make_uint4(0, 0, 0, 0);
   }
 }
 
@@ -557,13 +561,14 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
     if (ok) {
       const uint8_t *stage = sQt;
-      __nv_bfloat16 *obase = p.out + (int64_t)(q0 + T.m0) * p.o_tok_stride + (int64_t)T.h * p.o_head_stride;
+      const int64_t obase = (int64_t)(q0 + T.m0) * p.o_tok_stride + (int64_t)(p.out_head0 + T.h) * p.o_head_stride;
 #pragma unroll 4
       for (int it = 0; it < 16; ++it) {
         const int rr = it * 8 + (wtid >> 4), chunk = wtid & 15;
         if (rr < T.rows) {
           const uint4 v = *reinterpret_cast<const uint4 *>(stage + rr * 256 + ((chunk ^ (rr & 7)) << 4));
-          *reinterpret_cast<uint4 *>(obase + (int64_t)rr * p.o_tok_stride + chunk * 8) = v;
+          const int64_t off = obase + (int64_t)rr * p.o_tok_stride + chunk * 8;
+          for (int w = 0; w < p.world; ++w) *reinterpret_cast<uint4 *>(p.out[w] + off) = v;
         }
       }
     }
@@ -651,7 +656,8 @@ static char *launch_prefill(const char *fn, const CUtensorMap &tq, const CUtenso
 
 using namespace aici;
 
-extern "C" char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, const void *v,
+static char *mha_varlen_fwd_impl(const char *fn, void *const *outs, int world, int out_head0, const void *q,
+                                 const void *k, const void *v,
                                      const int32_t *cu_seqlens_q, const int32_t *cu_seqlens_k,
                                      int batch, int total_q, int total_k, int num_heads,
                                      int num_heads_k, int head_size, int max_seqlen_q,
@@ -661,7 +667,10 @@ extern "C" char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, co
                                      int64_t o_tok_stride, int64_t o_head_stride,
                                      float softmax_scale, int is_causal, int dtype,
                                      aici_stream_t stream) {
-  const char *fn = "aici_mha_varlen_fwd";
+  void *out = outs[0];
+  for (int w = 1; w < world; ++w)
+    AICI_CHECK(outs[w] != nullptr && (uintptr_t)outs[w] % 16 == 0,
+               "%s: peer output %d must be non-NULL and 16-byte aligned", fn, w);
   AICI_CHECK(dtype == AICI_DTYPE_BF16, "%s: FlashAttention only support bf16 data type (dtype=%d)", fn, dtype);
   AICI_CHECK(batch > 0, "%s: batch size must be positive", fn);
   AICI_CHECK(head_size == kHD, "%s: head_size must be 128 (got %d)", fn, head_size);
@@ -693,7 +702,9 @@ extern "C" char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, co
   if (char *e = make_tmap(fn, &tv, vv, tk_rows, num_heads_k, v_tok_stride, v_head_stride)) return e;
 
   PrefillParams p;
-  p.out = static_cast<__nv_bfloat16 *>(out);
+  for (int i = 0; i < 8; ++i) p.out[i] = static_cast<__nv_bfloat16 *>(i < world ? outs[i] : nullptr);
+  p.world = world;
+  p.out_head0 = out_head0;
   p.cu_q = cu_seqlens_q;
   p.cu_k = cu_seqlens_k;
   p.o_tok_stride = o_tok_stride;
@@ -708,6 +719,48 @@ extern "C" char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, co
   p.num_blocks = 0;
   return launch_prefill<false>(fn, tq, tk, tv, p, num_heads, batch, max_seqlen_q,
                                static_cast<cudaStream_t>(stream));
+}
+
+extern "C" char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, const void *v,
+                                     const int32_t *cu_seqlens_q, const int32_t *cu_seqlens_k,
+                                     int batch, int total_q, int total_k, int num_heads,
+                                     int num_heads_k, int head_size, int max_seqlen_q,
+                                     int max_seqlen_k, int64_t q_tok_stride, int64_t q_head_stride,
+                                     int64_t k_tok_stride, int64_t k_head_stride,
+                                     int64_t v_tok_stride, int64_t v_head_stride,
+                                     int64_t o_tok_stride, int64_t o_head_stride,
+                                     float softmax_scale, int is_causal, int dtype,
+                                     aici_stream_t stream) {
+  void *outs[1] = {out};
+  return mha_varlen_fwd_impl("aici_mha_varlen_fwd", outs, 1, 0, q, k, v, cu_seqlens_q, cu_seqlens_k, batch,
+                             total_q, total_k, num_heads, num_heads_k, head_size, max_seqlen_q,
+                             max_seqlen_k, q_tok_stride, q_head_stride, k_tok_stride, k_head_stride,
+                             v_tok_stride, v_head_stride, o_tok_stride, o_head_stride, softmax_scale,
+                             is_causal, dtype, stream);
+}
+
+// Prefill attention whose epilogue is the head-output gather: each finished output tile is stored
+// at head index head0 + h of the [total_q, total_heads, 128] buffer of EVERY rank (plain stores to
+// peer-mapped memory over NVLink, pushed tile by tile while later tiles are still computing), so
+// the gather hides under the attention math; the ranks only need a barrier before reading.
+extern "C" char *aici_mha_varlen_fwd_peers(void *const *outs, int world, int head0, const void *q,
+                                           const void *k, const void *v, const int32_t *cu_seqlens_q,
+                                           const int32_t *cu_seqlens_k, int batch, int total_q,
+                                           int total_k, int num_heads, int num_heads_k, int head_size,
+                                           int max_seqlen_q, int max_seqlen_k, int64_t q_tok_stride,
+                                           int64_t q_head_stride, int64_t k_tok_stride,
+                                           int64_t k_head_stride, int64_t v_tok_stride,
+                                           int64_t v_head_stride, int64_t o_tok_stride,
+                                           int64_t o_head_stride, float softmax_scale, int is_causal,
+                                           int dtype, aici_stream_t stream) {
+  const char *fn = "aici_mha_varlen_fwd_peers";
+  AICI_CHECK(outs != nullptr && world >= 1 && world <= 8, "%s: world must be 1..8", fn);
+  AICI_CHECK(head0 >= 0, "%s: negative head offset", fn);
+  return mha_varlen_fwd_impl(fn, outs, world, head0, q, k, v, cu_seqlens_q, cu_seqlens_k, batch, total_q,
+                             total_k, num_heads, num_heads_k, head_size, max_seqlen_q, max_seqlen_k,
+                             q_tok_stride, q_head_stride, k_tok_stride, k_head_stride, v_tok_stride,
+                             v_head_stride, o_tok_stride, o_head_stride, softmax_scale, is_causal, dtype,
+                             stream);
 }
 
 extern "C" char *aici_mha_varlen_paged_fwd(void *out, const void *q, const void *key_cache,
@@ -763,7 +816,9 @@ extern "C" char *aici_mha_varlen_paged_fwd(void *out, const void *q, const void 
     if (char *e = make_tmap_nd(fn, &tv, value_cache, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_32B)) return e;
   }
   PrefillParams p;
-  p.out = static_cast<__nv_bfloat16 *>(out);
+  for (int i = 0; i < 8; ++i) p.out[i] = i == 0 ? static_cast<__nv_bfloat16 *>(out) : nullptr;
+  p.world = 1;
+  p.out_head0 = 0;
   p.cu_q = cu_seqlens_q;
   p.cu_k = nullptr;
   p.o_tok_stride = o_tok_stride;

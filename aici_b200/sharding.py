@@ -70,3 +70,36 @@ def gather_heads(out_local: torch.Tensor, group=None, buffer: Optional[torch.Ten
     if not interleave:
         return buffer
     return buffer.permute(1, 0, 2, 3).reshape(tokens, world * h_local, d)
+
+
+class PeerGather:
+    """Output buffer [rows, total_heads, head_size] allocated in symmetric memory on every rank of
+    `group` and mapped into every peer's address space (torch.distributed symmetric memory over
+    NVLink).  The attention entry points `*_peers` store each rank's heads straight into all of
+    these buffers; `barrier()` (a signal exchange on the current stream, with a timeout) is the only
+    synchronisation before `tensor` holds all heads on every rank."""
+
+    def __init__(self, rows: int, total_heads: int, head_size: int, device, group=None,
+                 dtype=torch.bfloat16):
+        import torch.distributed._symmetric_memory as symm_mem
+        if not dist.is_initialized():
+            raise ShardingError("PeerGather needs an initialised process group")
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if total_heads % self.world != 0:
+            raise ShardingError("%d heads do not divide over %d ranks" % (total_heads, self.world))
+        self.total_heads = total_heads
+        self.heads_per_rank = total_heads // self.world
+        self.tensor = symm_mem.empty((rows, total_heads, head_size), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        self.ptrs = [int(x) for x in self.handle.buffer_ptrs]
+        if len(self.ptrs) != self.world or self.ptrs[self.rank] != self.tensor.data_ptr():
+            raise ShardingError("symmetric memory rendezvous returned unexpected buffer pointers")
+
+    @property
+    def head0(self) -> int:
+        return self.rank * self.heads_per_rank
+
+    def barrier(self, timeout_ms: int = 10000) -> None:
+        self.handle.barrier(channel=0, timeout_ms=timeout_ms)

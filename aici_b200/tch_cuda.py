@@ -442,3 +442,71 @@ def rotary_embedding_reshape_and_cache(positions: torch.Tensor, query: torch.Ten
             ctypes.c_int64(q2.stride(0)), ctypes.c_int64(k2.stride(0)), ctypes.c_int64(v2.stride(0)),
             ctypes.c_int(_dtype(fn, query)), _stream(dev))
     _lib.check(fn, res)
+
+
+def paged_attention_v1_peers(peer_ptrs: Sequence[int], total_heads: int, head0: int, query: torch.Tensor,
+                             key_cache: torch.Tensor, value_cache: torch.Tensor, num_kv_heads: int,
+                             scale: float, block_tables: torch.Tensor, context_lens: torch.Tensor,
+                             block_size: int, max_context_len: int) -> None:
+    """paged_attention_v1 whose output rows go to head index head0 + h of the
+    [num_seqs, total_heads, head_size] buffers at `peer_ptrs` (one device pointer per rank, this
+    rank's own included; see aici_b200.sharding.PeerGather).  No collective follows; ranks
+    synchronise before reading."""
+    fn = "paged_attention_v1_peers"
+    dev = _require_cuda(fn, query, key_cache, value_cache, block_tables, context_lens)
+    num_blocks, cache_kv_heads, head_size, cache_block = _cache_dims(fn, key_cache, value_cache)
+    if cache_kv_heads != num_kv_heads or cache_block != block_size:
+        raise AiciError("%s: num_kv_heads / block_size do not match the cache" % fn)
+    if query.dim() != 3 or query.shape[2] != head_size or query.stride(2) != 1 or query.stride(1) != head_size:
+        raise AiciError("%s: query rows must hold contiguous heads of the cache's head_size" % fn)
+    if block_tables.dtype != torch.int32 or context_lens.dtype != torch.int32 or \
+            not block_tables.is_contiguous() or not context_lens.is_contiguous():
+        raise AiciError("%s: block_tables and context_lens must be contiguous int32" % fn)
+    num_seqs, num_heads, _ = query.shape
+    world = len(peer_ptrs)
+    outs = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in peer_ptrs])
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        nbytes = L.aici_paged_attention_workspace_bytes(
+            ctypes.c_int(num_seqs), ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads),
+            ctypes.c_int(int(max_context_len)))
+        ws = _workspace(dev, nbytes)
+        res = L.aici_paged_attention_v1_peers(
+            outs, ctypes.c_int(world), ctypes.c_int(total_heads), ctypes.c_int(head0), _p(query),
+            _p(key_cache), _p(value_cache), ctypes.c_int(num_kv_heads), ctypes.c_float(scale),
+            _p(block_tables), _p(context_lens), ctypes.c_int(block_size), ctypes.c_int(int(max_context_len)),
+            ctypes.c_int(num_seqs), ctypes.c_int(num_heads), ctypes.c_int(head_size),
+            ctypes.c_int(block_tables.shape[1]), ctypes.c_int64(num_blocks), ctypes.c_int64(query.stride(0)),
+            ctypes.c_int64(key_cache.stride(0)), ctypes.c_int64(key_cache.stride(1)), _p(ws),
+            ctypes.c_size_t(ws.numel()), ctypes.c_int(_dtype(fn, query)), _stream(dev))
+    _lib.check(fn, res)
+
+
+def flash_attn_varlen_peers(peer_ptrs: Sequence[int], total_heads: int, head0: int, q: torch.Tensor,
+                            k: torch.Tensor, v: torch.Tensor, seqlens_q: torch.Tensor,
+                            seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int,
+                            softmax_scale: float, causal: bool) -> None:
+    """flash_attn_varlen whose output tiles go to head index head0 + h of the contiguous
+    [total_q, total_heads, head_size] buffers at `peer_ptrs` (one per rank, own included)."""
+    fn = "flash_attn_varlen_peers"
+    dev = _require_cuda(fn, q, k, v, seqlens_q, seqlens_k)
+    if seqlens_q.dtype != torch.int32 or seqlens_k.dtype != torch.int32:
+        raise AiciError("%s: cu_seqlens must have dtype int32" % fn)
+    for t in (q, k, v):
+        if t.dim() != 3 or t.stride(-1) != 1:
+            raise AiciError("%s: q, k, v must be 3-D with contiguous last dimension" % fn)
+    total_q, num_heads, head_size = q.shape
+    batch = seqlens_q.numel() - 1
+    world = len(peer_ptrs)
+    outs = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in peer_ptrs])
+    with torch.cuda.device(dev):
+        res = _lib.lib().aici_mha_varlen_fwd_peers(
+            outs, ctypes.c_int(world), ctypes.c_int(head0), _p(q), _p(k), _p(v), _p(seqlens_q), _p(seqlens_k),
+            ctypes.c_int(batch), ctypes.c_int(total_q), ctypes.c_int(k.shape[0]), ctypes.c_int(num_heads),
+            ctypes.c_int(k.shape[1]), ctypes.c_int(head_size), ctypes.c_int(int(max_seqlen_q)),
+            ctypes.c_int(int(max_seqlen_k)), ctypes.c_int64(q.stride(0)), ctypes.c_int64(q.stride(1)),
+            ctypes.c_int64(k.stride(0)), ctypes.c_int64(k.stride(1)), ctypes.c_int64(v.stride(0)),
+            ctypes.c_int64(v.stride(1)), ctypes.c_int64(total_heads * head_size), ctypes.c_int64(head_size),
+            ctypes.c_float(softmax_scale), ctypes.c_int(1 if causal else 0), ctypes.c_int(_dtype(fn, q)),
+            _stream(dev))
+    _lib.check(fn, res)

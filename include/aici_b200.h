@@ -181,6 +181,33 @@ char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, const void *v
                           int64_t o_tok_stride, int64_t o_head_stride, float softmax_scale,
                           int is_causal, int dtype, aici_stream_t stream);
 
+/* ---- multi-GPU: attention whose epilogue is the head-output gather -------------------------
+ * The reference has no multi-GPU code; its only hook is the per-rank kv-head count
+ * (rllm-cuda/src/llm/config.rs:49-51).  With kv heads sharded over the GPUs of one box every rank
+ * needs all heads of the attention output afterwards.  These two entry points write each finished
+ * output row / tile straight into the output buffer of EVERY rank (outs[0..world), peer-mapped
+ * device pointers, this rank's own included; each buffer [rows, total_heads, 128]) at head index
+ * head0 + h, so no collective follows: the ranks only synchronise (a barrier) before reading.
+ * Everything else is as in aici_paged_attention_v1 / aici_mha_varlen_fwd. */
+char *aici_paged_attention_v1_peers(void *const *outs, int world, int total_heads, int head0,
+                                    const void *query, const void *key_cache,
+                                    const void *value_cache, int num_kv_heads, float scale,
+                                    const int32_t *block_tables, const int32_t *context_lens,
+                                    int block_size, int max_context_len, int num_seqs,
+                                    int num_heads, int head_size, int max_num_blocks_per_seq,
+                                    int64_t num_blocks, int64_t q_stride, int64_t kv_block_stride,
+                                    int64_t kv_head_stride, void *workspace, size_t workspace_bytes,
+                                    int dtype, aici_stream_t stream);
+
+char *aici_mha_varlen_fwd_peers(void *const *outs, int world, int head0, const void *q,
+                                const void *k, const void *v, const int32_t *cu_seqlens_q,
+                                const int32_t *cu_seqlens_k, int batch, int total_q, int total_k,
+                                int num_heads, int num_heads_k, int head_size, int max_seqlen_q,
+                                int max_seqlen_k, int64_t q_tok_stride, int64_t q_head_stride,
+                                int64_t k_tok_stride, int64_t k_head_stride, int64_t v_tok_stride,
+                                int64_t v_head_stride, int64_t o_tok_stride, int64_t o_head_stride,
+                                float softmax_scale, int is_causal, int dtype, aici_stream_t stream);
+
 /* Variable-length causal prefill that reads keys and values straight from the paged cache.
  * Replaces the sequence gather_cached_kv -> repeat_kv -> flash_attn_varlen of
  * compute_varlen_attn (rllm-cuda/src/llm/mod.rs:168-278; kernels/vllm/cache_kernels.cu:301-413):

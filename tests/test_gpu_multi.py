@@ -41,6 +41,15 @@ def _worker(rank, world, port, q):
             tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
                                         w.block_tables, w.context_lens, 16, w.max_context_len, None)
             full = sharding.gather_heads(out)
+            # the same through the fused epilogue: rows stored straight into every rank's buffer
+            pg = sharding.PeerGather(w.query.shape[0], kw["num_heads"], 128, dev)
+            pg.barrier()
+            tch_cuda.paged_attention_v1_peers(pg.ptrs, kw["num_heads"], pg.head0, w.query, w.key_cache,
+                                              w.value_cache, w.num_kv_heads, w.scale, w.block_tables,
+                                              w.context_lens, 16, w.max_context_len)
+            pg.barrier()
+            torch.cuda.synchronize()
+            assert torch.equal(pg.tensor.view(torch.int16), full.contiguous().view(torch.int16)), name + " fused gather"
             if rank == 0:
                 from oracle import cpu_oracle as O
                 f = workloads.make_decode(name, dev, **kw)  # unsharded, same seed
@@ -56,6 +65,13 @@ def _worker(rank, world, port, q):
             o = tch_cuda.flash_attn_varlen(w.q, w.k, w.v, w.cu_seqlens_q, w.cu_seqlens_k, w.max_seqlen_q,
                                            w.max_seqlen_k, w.scale, True)
             full = sharding.gather_heads(o)
+            pg = sharding.PeerGather(w.q.shape[0], kw["num_heads"], 128, dev)
+            pg.barrier()
+            tch_cuda.flash_attn_varlen_peers(pg.ptrs, kw["num_heads"], pg.head0, w.q, w.k, w.v, w.cu_seqlens_q,
+                                             w.cu_seqlens_k, w.max_seqlen_q, w.max_seqlen_k, w.scale, True)
+            pg.barrier()
+            torch.cuda.synchronize()
+            assert torch.equal(pg.tensor.view(torch.int16), full.contiguous().view(torch.int16)), name + " fused gather"
             if rank == 0:
                 from oracle import cpu_oracle as O
                 f = workloads.make_prefill(name, dev, **kw)
