@@ -28,6 +28,7 @@ EXPORTS = (
     "aici_mha_varlen_paged_fwd",
     "aici_paged_attention_v1_peers",
     "aici_mha_varlen_fwd_peers",
+    "aici_peer_barrier",
 )
 
 _lib = None

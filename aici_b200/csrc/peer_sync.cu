@@ -1,0 +1,55 @@
+// Cross-GPU barrier for the fused head-output gather: after a rank's attention kernels have
+// stored their rows into every peer's output buffer, the ranks only need to know that everybody
+// is done.  One warp per rank: lane p publishes this rank's epoch into peer p's flag array (a
+// release store at system scope, after the preceding kernels of the stream have completed) and
+// then waits -- bounded -- until peer p's epoch shows up in its own array.  Flags live in
+// peer-mapped symmetric memory; epochs only grow, so nothing is ever reset.
+#include "common.cuh"
+
+namespace aici {
+
+struct PeerFlags {
+  unsigned int *flags[8];  // flags[p] = rank p's array of 8 slots (slot r is written by rank r)
+};
+
+__global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerFlags f, int world, int rank,
+                                                          unsigned int epoch, unsigned int *status) {
+  const int p = threadIdx.x;
+  if (p >= world) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f.flags[p] + rank), "r"(epoch) : "memory");
+  const unsigned int *mine = f.flags[rank] + p;
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int)(v - epoch) >= 0) break;
+    if (clock64() - t0 > (1ll << 31)) {  // about a second: give up, report, keep the context usable
+      set_status(status, AICI_STATUS_WAIT_TIMEOUT);
+      break;
+    }
+  }
+}
+
+}  // namespace aici
+
+using namespace aici;
+
+extern "C" char *aici_peer_barrier(void *const *flag_ptrs, int world, int rank, unsigned int epoch,
+                                   aici_stream_t stream) {
+  const char *fn = "aici_peer_barrier";
+  AICI_CHECK(flag_ptrs != nullptr && world >= 1 && world <= 8 && rank >= 0 && rank < world,
+             "%s: world must be 1..8 and rank inside it", fn);
+  if (world == 1) return nullptr;
+  unsigned int *st = status_ptr();
+  AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
+  PeerFlags f;
+  for (int i = 0; i < 8; ++i) {
+    f.flags[i] = static_cast<unsigned int *>(i < world ? flag_ptrs[i] : nullptr);
+    AICI_CHECK(i >= world || (f.flags[i] != nullptr && (uintptr_t)f.flags[i] % 4 == 0),
+               "%s: flag array %d must be non-NULL and 4-byte aligned", fn, i);
+  }
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, world, rank, epoch, st);
+  AICI_CUDA(cudaGetLastError());
+  return nullptr;
+}

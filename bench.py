@@ -219,13 +219,30 @@ def run_ours(args):
     gathered = torch.empty(world, S, hq_local, 128, dtype=torch.bfloat16, device=dev) if world > 1 else None
     step_bytes_local = w.algorithmic_bytes() + w.cache_write_bytes()
     decode_bytes_local = w.algorithmic_bytes()
+    fused = world > 1 and args.gather == "fused"
+    pg = None
+    if fused:
+        from aici_b200 import sharding
+        pg = sharding.PeerGather(S, hq_local * world, 128, dev)
+        pg.barrier()
+
+    def attention(q, bt, cl):
+        """decode attention + head gather: fused epilogue (peer stores + barrier) or NCCL all-gather"""
+        if fused:
+            tch_cuda.paged_attention_v1_peers(pg.ptrs, hq_local * world, pg.head0, q, w.key_cache, w.value_cache,
+                                              w.num_kv_heads, w.scale, bt, cl, 16, w.max_context_len)
+            pg.barrier()
+            return pg.tensor
+        tch_cuda.paged_attention_v1(out, q, w.key_cache, w.value_cache, w.num_kv_heads, w.scale, bt, cl, 16,
+                                    w.max_context_len, None)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), out)
+            return gathered
+        return out
 
     def step():
         tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
-        tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
-                                    w.block_tables, w.context_lens, 16, w.max_context_len, None)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), out)
+        attention(w.query, w.block_tables, w.context_lens)
 
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
@@ -239,10 +256,17 @@ def run_ours(args):
     for i in range(args.steps):
         tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
         att_ev[i][0].record()
-        tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
-                                    w.block_tables, w.context_lens, 16, w.max_context_len, None)
+        if fused:
+            tch_cuda.paged_attention_v1_peers(pg.ptrs, hq_local * world, pg.head0, w.query, w.key_cache,
+                                              w.value_cache, w.num_kv_heads, w.scale, w.block_tables,
+                                              w.context_lens, 16, w.max_context_len)
+        else:
+            tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                        w.block_tables, w.context_lens, 16, w.max_context_len, None)
         att_ev[i][1].record()
-        if world > 1:
+        if fused:
+            pg.barrier()
+        elif world > 1:
             dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), out)
     ev1.record()
     barrier()
@@ -261,18 +285,16 @@ def run_ours(args):
         "slots": w.slot_mapping.cpu().pin_memory(), "bt": w.block_tables.cpu().pin_memory(),
         "cl": w.context_lens.cpu().pin_memory(),
     }
-    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    host_out = torch.empty((S, hq_local * world, 128) if world > 1 else out.shape, dtype=out.dtype).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in host.values())
     d2h = host_out.numel() * host_out.element_size()
 
     def e2e_step():
         d = {k: t.to(dev, non_blocking=True) for k, t in host.items()}
         tch_cuda.reshape_and_cache(d["nk"], d["nv"], w.key_cache, w.value_cache, d["slots"])
-        o = torch.empty_like(d["q"])
-        tch_cuda.paged_attention_v1(o, d["q"], w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
-                                    d["bt"], d["cl"], 16, w.max_context_len, None)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), o)
+        o = attention(d["q"], d["bt"], d["cl"])
+        if world > 1 and not fused:
+            o = o.permute(1, 0, 2, 3).reshape(S, hq_local * world, 128)
         host_out.copy_(o, non_blocking=True)
 
     for _ in range(max(3, args.warmup // 2)):
@@ -297,13 +319,26 @@ def run_ours(args):
         return tch_cuda.flash_attn_varlen(pw.q, pw.k, pw.v, pw.cu_seqlens_q, pw.cu_seqlens_k,
                                           pw.max_seqlen_q, pw.max_seqlen_k, pw.scale, True)
 
-    pg = None
-    if world > 1:
-        pg = torch.empty(world, pw.q.shape[0], pw.q.shape[1], 128, dtype=torch.bfloat16, device=dev)
+    pbuf, ppg = None, None
+    if fused:
+        ppg = sharding.PeerGather(pw.q.shape[0], pw.q.shape[1] * world, 128, dev)
+        ppg.barrier()
+
+        def pstep():  # noqa: F811
+            tch_cuda.flash_attn_varlen_peers(ppg.ptrs, pw.q.shape[1] * world, ppg.head0, pw.q, pw.k, pw.v,
+                                             pw.cu_seqlens_q, pw.cu_seqlens_k, pw.max_seqlen_q,
+                                             pw.max_seqlen_k, pw.scale, True)
+            return ppg.tensor
+    elif world > 1:
+        pbuf = torch.empty(world, pw.q.shape[0], pw.q.shape[1], 128, dtype=torch.bfloat16, device=dev)
+
+    def pgather(o):
+        if fused:
+            ppg.barrier()
+        elif world > 1:
+            dist.all_gather_into_tensor(pbuf.view(-1, pbuf.shape[2], 128), o)
     for _ in range(p_warm):
-        o = pstep()
-        if world > 1:
-            dist.all_gather_into_tensor(pg.view(-1, pg.shape[2], 128), o)
+        pgather(pstep())
     barrier()
     k_ms = []
     ev0.record()
@@ -313,8 +348,7 @@ def run_ours(args):
         o = pstep()
         b.record()
         k_ms.append((a, b))
-        if world > 1:
-            dist.all_gather_into_tensor(pg.view(-1, pg.shape[2], 128), o)
+        pgather(o)
     ev1.record()
     barrier()
     p_ms = max_over_ranks(ev0.elapsed_time(ev1)) / p_steps
@@ -345,7 +379,10 @@ def run_ours(args):
             "l2": "no flush: each step streams %.2f GB of K/V per GPU, far above the 126 MB L2" % (
                 decode_bytes_local / 1e9),
             "algorithmic_bytes_per_step": step_bytes_local * world,
-            "collective": "nccl all_gather of head outputs" if world > 1 else "none",
+            "collective": ("none" if world == 1 else
+                           "fused: attention epilogue stores head outputs into every rank's buffer over "
+                           "NVLink (peer-mapped symmetric memory), then a signal barrier" if fused else
+                           "nccl all_gather of head outputs"),
         },
         "roofline": {
             "kernel": "paged_decode_kernel (+ plan and merge launches of the same call)",
@@ -578,6 +615,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="multi-GPU head-output gather: fused into the attention epilogue (default) or NCCL")
     ap.add_argument("--suite", action="store_true",
                     help="time all five configurations at the current world size and print one JSON object")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
