@@ -96,12 +96,11 @@ class PeerGather:
         self.ptrs = [int(x) for x in self.handle.buffer_ptrs]
         if len(self.ptrs) != self.world or self.ptrs[self.rank] != self.tensor.data_ptr():
             raise ShardingError("symmetric memory rendezvous returned unexpected buffer pointers")
-        # flags of the library's own barrier kernel: 8 slots per rank, zero, peer-mapped
-        self._flags = symm_mem.empty((8,), dtype=torch.int32, device=device)
+        # flags of the library's own barrier kernel: 16 slots per rank, zero, peer-mapped
+        self._flags = symm_mem.empty((16,), dtype=torch.int32, device=device)
         self._flags.zero_()
         self._flag_handle = symm_mem.rendezvous(self._flags, self.group)
         self._flag_ptrs = [int(x) for x in self._flag_handle.buffer_ptrs]
-        self._epoch = 0
         torch.cuda.synchronize(device)
         self.handle.barrier(channel=0, timeout_ms=60000)  # every rank's flags are zero before first use
 
@@ -113,11 +112,9 @@ class PeerGather:
         """Enqueue the cross-rank barrier on the current stream (bounded wait on the device)."""
         import ctypes
         from . import _lib
-        self._epoch += 1
         arr = (ctypes.c_void_p * self.world)(*[ctypes.c_void_p(x) for x in self._flag_ptrs])
         dev = self.tensor.device
         with torch.cuda.device(dev):
             res = _lib.lib().aici_peer_barrier(arr, ctypes.c_int(self.world), ctypes.c_int(self.rank),
-                                               ctypes.c_uint(self._epoch),
                                                ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
         _lib.check("peer_barrier", res)

@@ -209,12 +209,12 @@ char *aici_mha_varlen_fwd_peers(void *const *outs, int world, int head0, const v
                                 float softmax_scale, int is_causal, int dtype, aici_stream_t stream);
 
 /* Barrier between the ranks that share peer-mapped buffers (no counterpart in the reference).
- * flag_ptrs[p] = rank p's array of 8 uint32 slots in peer-mapped memory, zero at start; every
- * rank calls with the same, strictly growing `epoch`.  Enqueued on `stream`: work queued after
- * it starts once every rank's earlier work on its own stream has finished.  The wait is bounded
- * (about a second), then AICI_STATUS_WAIT_TIMEOUT is recorded. */
-char *aici_peer_barrier(void *const *flag_ptrs, int world, int rank, unsigned int epoch,
-                        aici_stream_t stream);
+ * flag_ptrs[p] = rank p's array of 16 uint32 slots in peer-mapped memory, all zero before the
+ * first call; every rank must call it the same number of times (the epoch is a counter kept in the
+ * array, so a captured launch can be replayed).  Enqueued on `stream`: work queued after it starts
+ * once every rank's earlier work on its own stream has finished.  The wait is bounded (about a
+ * second), then AICI_STATUS_WAIT_TIMEOUT is recorded. */
+char *aici_peer_barrier(void *const *flag_ptrs, int world, int rank, aici_stream_t stream);
 
 /* Variable-length causal prefill that reads keys and values straight from the paged cache.
  * Replaces the sequence gather_cached_kv -> repeat_kv -> flash_attn_varlen of
