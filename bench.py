@@ -295,7 +295,6 @@ def run_ours(args):
             pg.barrier()
         elif world > 1:
             dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), out)
-    evx.record()
     barrier()
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     ms_step = ms_total / args.steps
