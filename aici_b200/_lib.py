@@ -29,6 +29,9 @@ EXPORTS = (
     "aici_paged_attention_v1_peers",
     "aici_mha_varlen_fwd_peers",
     "aici_peer_barrier",
+    "aici_swap_blocks",
+    "aici_batch_info_layout",
+    "aici_batch_info_build",
 )
 
 _lib = None

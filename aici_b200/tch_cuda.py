@@ -236,6 +236,43 @@ def copy_blocks_2(key_cache_ptrs_tensor: torch.Tensor, value_cache_ptrs_tensor: 
     _lib.check(fn, res)
 
 
+def swap_blocks(src: torch.Tensor, dst: torch.Tensor, block_mapping) -> None:
+    """`kernels::swap_blocks(src, dst, src_to_dst, stream)` as CacheEngine::swap calls it per layer
+    for K and for V (rllm-cuda/src/llm/paged/cache_engine.rs:139-149; C side
+    kernels/vllm/cache_kernels.cu:12-50): dst[d] = src[s] for every s -> d of `block_mapping`
+    (dict, or a flat int64 CPU tensor of (src, dst) pairs).  Either tensor may live in host memory
+    (page-locked: one kernel launch over PCIe; pageable: copy engine); at least one is on the GPU.
+    Runs on the current stream of the CUDA tensor's device."""
+    fn = "swap_blocks"
+    if src.dim() < 1 or dst.dim() < 1 or src.shape[1:] != dst.shape[1:] or src.dtype != dst.dtype:
+        raise AiciError("%s: src and dst must have the same block shape and dtype" % fn)
+    if not src.is_contiguous() or not dst.is_contiguous():
+        raise AiciError("%s: caches must be contiguous" % fn)
+    cuda = [t for t in (src, dst) if t.is_cuda]
+    if not cuda:
+        raise AiciError("%s: Invalid device combination" % fn)
+    if len(cuda) == 2 and src.device != dst.device:
+        raise AiciError("%s: src and dst must be on the same GPU" % fn)
+    if isinstance(block_mapping, torch.Tensor):
+        pairs = block_mapping.to(torch.int64).contiguous().view(-1)
+        if pairs.is_cuda:
+            raise AiciError("%s: block_mapping must be a CPU tensor" % fn)
+    else:
+        flat: List[int] = []
+        for s, d in block_mapping.items():
+            flat += [int(s), int(d)]
+        pairs = torch.tensor(flat, dtype=torch.int64)
+    if pairs.numel() == 0:
+        return
+    dev = cuda[0].device
+    block_bytes = src[0].numel() * src.element_size()
+    with torch.cuda.device(dev):
+        _lib.check(fn, _lib.lib().aici_swap_blocks(
+            _p(src), _p(dst), ctypes.c_void_p(pairs.data_ptr()), ctypes.c_int(pairs.numel() // 2),
+            ctypes.c_int64(block_bytes), ctypes.c_int64(src.shape[0]), ctypes.c_int64(dst.shape[0]),
+            _stream(dev)))
+
+
 def _decode_common(fn, out, query, key_cache, value_cache, num_kv_heads, block_tables,
                    context_lens, block_size):
     dev = _require_cuda(fn, out, query, key_cache, value_cache, block_tables, context_lens)

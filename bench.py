@@ -497,12 +497,15 @@ def run_suite(args):
         if kind == "hbm":
             ach = work_local / (k_ms * 1e-3) / 1e9
             peak, unit = peaks["hbm_gbs"], "GB/s"
+        elif kind == "pcie":  # host <-> device traffic: no measured peak on file, fraction omitted
+            ach = work_local / (k_ms * 1e-3) / 1e9
+            peak, unit = None, "GB/s"
         else:
             ach = work_local / (k_ms * 1e-3) / 1e12
             peak, unit = peaks["bf16_tflops_sustained"], "TFLOP/s"
         row = {"config": name, "n_gpus": world, "kernel_ms": k_ms, "gather_ms": g_ms,
                "work_per_gpu": work_local, "work_total": total, "achieved_per_gpu": ach, "unit": unit,
-               "frac_of_peak": ach / peak, "aggregate": ach * world,
+               "frac_of_peak": (ach / peak if peak else None), "aggregate": ach * world,
                "aggregate_with_gather": work_local * world / ((k_ms + g_ms) * 1e-3) / (1e9 if kind == "hbm" else 1e12)}
         if extra:
             row.update(extra)
@@ -596,6 +599,57 @@ def run_suite(args):
                                                              pw.scale, True))
     add("next: paged prefill 2x%d (K/V read through block tables)" % L, "tensor", pw.flops(), k_ms, 0.0)
     del pw, kc, vc, kg, vg
+
+    # swap_blocks (the "next" row): 1024 blocks of one layer's K cache out to page-locked host memory
+    # and back in, one launch each, against one cudaMemcpyAsync per block (the reference's way)
+    hkv = max(1, 8 // world)
+    nblk = 2048
+    kc = torch.randn(nblk, hkv, 16, 16, 8, device=dev).to(torch.bfloat16)
+    host = torch.empty(nblk, hkv, 16, 16, 8, dtype=torch.bfloat16).pin_memory()
+    gsel = torch.randperm(nblk)[:1024]
+    hsel = torch.randperm(nblk)[:1024]
+    out_pairs = torch.stack([gsel, hsel], 1).reshape(-1).to(torch.int64)
+    in_pairs = torch.stack([hsel, gsel], 1).reshape(-1).to(torch.int64)
+    blk_bytes = hkv * 128 * 16 * 2
+    o_ms, _ = timed(lambda: tch_cuda.swap_blocks(kc, host, out_pairs))
+    add("next: swap_blocks out, 1024 blocks of %d KB to page-locked host" % (blk_bytes >> 10), "pcie",
+        1024 * blk_bytes, o_ms, 0.0)
+    i_ms, _ = timed(lambda: tch_cuda.swap_blocks(host, kc, in_pairs))
+    add("next: swap_blocks in, 1024 blocks of %d KB from page-locked host" % (blk_bytes >> 10), "pcie",
+        1024 * blk_bytes, i_ms, 0.0)
+
+    def per_block_copies():
+        for s_, d_ in zip(gsel.tolist(), hsel.tolist()):
+            host[d_].copy_(kc[s_], non_blocking=True)
+    m_ms, _ = timed(per_block_copies)
+    add("next: (comparison) one async copy per block, same 1024 blocks out", "pcie", 1024 * blk_bytes, m_ms, 0.0)
+    del kc, host
+
+    # BatchInfo staging (the "next" row): config 3's decode step (256 sequences) described as
+    # entries, built natively into one page-locked buffer and uploaded with one copy; host wall time
+    from aici_b200 import batch_info
+    w = workloads.decode_llama3_8b(dev, shard=shard)
+    tables = w.block_tables.cpu()
+    offs = torch.arange(16, dtype=torch.int64)
+    ent = []
+    for i, c in enumerate(w.context_list):
+        blocks = tables[i, :(c + 15) // 16].to(torch.int64)
+        ent.append((i, torch.tensor([7], dtype=torch.int32), (blocks[:, None] * 16 + offs[None, :]).reshape(-1)[:c].contiguous()))
+    bld = batch_info.BatchInfoBuilder(block_size=16, max_model_len=1 << 20, device=dev, gather_mapping=False)
+    walls = []
+    for it in range(warm + iters):
+        for sid, tok, sl in ent:
+            bld.add_arrays(sid, tok, sl)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        bi = bld.finish(it)
+        torch.cuda.synchronize()
+        walls.append((time.perf_counter() - t0) * 1e3)
+    assert torch.equal(bi.paged_context_lens, w.context_lens)
+    rows.append({"config": "next: BatchInfo build + one upload, config 3 decode step (256 sequences)",
+                 "n_gpus": world, "host_wall_ms": statistics.median(walls[warm:]),
+                 "bytes_uploaded": int(bi.layout.total_bytes), "uploads": 1})
+    del w, bld, bi, ent
 
     # config 4: long prefill
     pw = workloads.prefill_long(dev, shard=shard)

@@ -188,6 +188,8 @@ char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, const void *v
  * output row / tile straight into the output buffer of EVERY rank (outs[0..world), peer-mapped
  * device pointers, this rank's own included; each buffer [rows, total_heads, 128]) at head index
  * head0 + h, so no collective follows: the ranks only synchronise (a barrier) before reading.
+ * A peer may start the next call while this rank still reads the buffer, so a caller either
+ * alternates between two output buffers or places a second barrier after the readers.
  * Everything else is as in aici_paged_attention_v1 / aici_mha_varlen_fwd. */
 char *aici_paged_attention_v1_peers(void *const *outs, int world, int total_heads, int head0,
                                     const void *query, const void *key_cache,
@@ -234,6 +236,85 @@ char *aici_mha_varlen_paged_fwd(void *out, const void *q, const void *key_cache,
                                 int64_t q_head_stride, int64_t o_tok_stride, int64_t o_head_stride,
                                 int64_t kv_block_stride, int64_t kv_head_stride, float softmax_scale,
                                 int is_causal, int dtype, aici_stream_t stream);
+
+/* ---- swap_blocks ---------------------------------------------------------------------------
+ * Replaces swap_blocks (rllm/tch-cuda/kernels/vllm/cache_kernels.cu:12-50), which rLLM's
+ * CacheEngine::swap calls per layer for K and for V (rllm-cuda/src/llm/paged/cache_engine.rs:139-149)
+ * and which issues one cudaMemcpyAsync per block.  dst[block d] = src[block s] for every (s, d) of
+ * block_mapping_host (host array of 2*num_pairs int64).  src and dst are the bases of two caches of
+ * block_bytes-sized blocks; where each lives is read from the pointer itself: device <-> device on
+ * one GPU, device <-> page-locked host (one kernel launch moves all blocks over PCIe), or
+ * device <-> pageable host (copy engine, one transfer per run of consecutive blocks).  Host <-> host
+ * is refused ("Invalid device combination"), two different GPUs too, as in the reference.
+ * Stream-ordered; a host-side cache must stay untouched until the stream reaches the call. */
+char *aici_swap_blocks(const void *src, void *dst, const int64_t *block_mapping_host, int num_pairs,
+                       int64_t block_bytes, int64_t src_num_blocks, int64_t dst_num_blocks,
+                       aici_stream_t stream);
+
+/* ---- BatchInfo staging ---------------------------------------------------------------------
+ * Replaces BatchInfoBuilder::finish (rllm-cuda/src/llm/paged/batch_info.rs:196-315): from the
+ * running sequences of one step it builds tokens, positions, slot_mapping, logit_idxs, the
+ * cu_seqlens of the multi-token entries, gather_mapping, and the block tables and context lengths
+ * of the single-token entries.  The reference makes nine Vecs and uploads each with its own
+ * Tensor::from_slice(..).to(device); here all sections are written into ONE caller-owned staging
+ * buffer (page-locked host memory) at 256-byte aligned offsets and reach the device with ONE
+ * cudaMemcpyAsync.  slot_mapping stays int32 (aici_reshape_and_cache accepts it, so the per-layer
+ * int64 cast of lib.rs:199-200 is gone). */
+typedef struct aici_batch_entry {
+  int64_t seq_id;
+  const int32_t *tokens;    /* q_len token ids */
+  const int64_t *positions; /* q_len positions, or NULL for k_len - q_len .. k_len - 1 */
+  const int64_t *kv_slots;  /* k_len cache slots of the whole sequence (block * block_size + off) */
+  int32_t q_len;            /* query tokens of this step, >= 1 */
+  int32_t k_len;            /* context length including the query tokens, >= q_len */
+} aici_batch_entry;
+
+enum {
+  AICI_BATCH_PAGED_DECODE = 1,   /* paged_attn_kernel_v > 0: single-token entries go to the back
+                                    and get block tables instead of gather_mapping entries */
+  AICI_BATCH_TABLES_FOR_ALL = 2, /* block tables and context lengths for the multi-token entries
+                                    too (rows 0 .. num_multitoken), for aici_mha_varlen_paged_fwd */
+  AICI_BATCH_NO_GATHER_MAP = 4   /* leave gather_mapping empty (nothing calls gather_cached_kv) */
+};
+
+typedef struct aici_batch_layout {
+  int64_t total_bytes; /* size of the staging buffer and of the device copy */
+  /* byte offsets of the sections; element types in the comments */
+  int64_t tokens_off;         /* int32 [num_tokens] */
+  int64_t positions_off;      /* int64 [num_tokens] */
+  int64_t slot_mapping_off;   /* int32 [num_tokens] */
+  int64_t logit_idxs_off;     /* int32 [num_entries] */
+  int64_t seqlens_q_off;      /* int32 [num_multitoken + 1], offsets into tokens */
+  int64_t seqlens_k_off;      /* int32 [num_multitoken + 1] */
+  int64_t gather_mapping_off; /* int32 [gather_len] */
+  int64_t block_tables_off;   /* int32 [table_rows, max_blocks_per_seq], rows zero-padded */
+  int64_t context_lens_off;   /* int32 [table_rows] */
+  int32_t num_entries, num_tokens;
+  int32_t num_multitoken; /* BatchInfo::seqlen_multi */
+  int32_t q_multi;        /* BatchInfo::q_multi: tokens before the first single-token entry */
+  int32_t max_seqlen_q, max_seqlen_k;
+  int32_t gather_len;
+  int32_t num_paged;  /* single-token entries served by the paged decode kernel */
+  int32_t table_rows; /* num_paged, or num_entries with AICI_BATCH_TABLES_FOR_ALL */
+  int32_t paged_row0; /* first row of the single-token entries in block_tables / context_lens */
+  int32_t max_blocks_per_seq;
+  int32_t paged_max_context_len;
+} aici_batch_layout;
+
+/* Sizes and offsets only; touches no buffer.  Errors mirror the reference's asserts: no entry at
+ * all, a position >= max_model_len, a block-start slot that is not a multiple of block_size. */
+char *aici_batch_info_layout(const aici_batch_entry *entries, int num_entries, int flags,
+                             int block_size, int64_t max_model_len, aici_batch_layout *layout);
+
+/* Fills `staging` (host memory, at least layout->total_bytes; page-locked for an asynchronous
+ * copy) and, when device_dst is not NULL, enqueues one host-to-device copy of total_bytes on
+ * `stream`.  entry_order[i] (optional, num_entries ints) = index in `entries` of the sequence
+ * placed at batch index i, i.e. BatchInfo::seq_id_to_idx inverted.  staging must not be rewritten
+ * before the stream has passed the copy. */
+char *aici_batch_info_build(const aici_batch_entry *entries, int num_entries, int flags,
+                            int block_size, int64_t max_model_len, void *staging,
+                            size_t staging_bytes, void *device_dst, size_t device_bytes,
+                            aici_batch_layout *layout, int32_t *entry_order, aici_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -81,6 +81,16 @@ def copy_blocks(key_caches, value_caches, block_mapping):
                              ctypes.c_int64(numel))
 
 
+def swap_blocks(src, dst, block_mapping):
+    """dst[d] = src[s] for every s -> d, in ascending order of s as std::map iterates
+    (cache_kernels.cu:12-50).  Both CPU tensors of shape [num_blocks, ...]."""
+    pairs = sorted(block_mapping.items()) if isinstance(block_mapping, dict) else [
+        (int(block_mapping[2 * i]), int(block_mapping[2 * i + 1]))
+        for i in range(len(block_mapping) // 2)]
+    for s, d in pairs:
+        dst[d].copy_(src[s])
+
+
 def _paged_common(query, key_cache, value_cache, block_tables, context_lens):
     num_seqs, num_heads, head_size = query.shape
     assert query.stride(2) == 1 and query.stride(1) == head_size
