@@ -56,6 +56,8 @@ struct DecodeParams {
   int max_parts;
   int always_write_partials;  // v2 calling convention: partials are an output too
   int inline_plan;            // 1: every CTA builds the chunk prefix sums itself (no plan kernel)
+  int *span_cum;              // spans mode: [num_seqs + 2] tile prefix sums, then the span length
+  int min_span;               // spans mode: fewest tiles a warp takes
   int64_t q_stride, kv_block_stride, kv_head_stride;
   float scale_log2e;
   unsigned int *status;
@@ -63,6 +65,15 @@ struct DecodeParams {
 
 struct Item {
   int seq, chunk, kvh, ctx, tok0, ntiles;
+  int single;     // the (sequence, kv head) row has no other piece: write the final row
+  int pstep;      // distance between the partials of consecutive heads of the group
+  int64_t pbase;  // index of the partial of the group's first head
+};
+
+// Spans mode: position in the global tile order (sequence-major, then kv head, then tile) and the
+// end of this warp's span.
+struct Cursor {
+  int x, end;
 };
 
 __device__ __forceinline__ int clamp_ctx(const DecodeParams &p, int ctx) {
@@ -103,6 +114,46 @@ __device__ __forceinline__ void fetch_item(const DecodeParams &p, const int *s_c
   int n = it.ctx - it.tok0;
   if (n > p.chunk_tokens) n = p.chunk_tokens;
   it.ntiles = n > 0 ? (n + kB - 1) / kB : 0;
+  it.single = it.ctx <= p.chunk_tokens;
+  it.pstep = p.max_parts;
+  it.pbase = ((int64_t)it.seq * p.num_heads + it.kvh * p.group) * p.max_parts + it.chunk;
+}
+
+// Spans mode.  All tiles of the batch form one sequence: row (seq, kvh) starts at global tile
+// num_kv_heads * cum[seq] + kvh * tiles(seq), cum = tile prefix sums over the batch (s_cum).
+// Every warp owns `span` consecutive global tiles, so all warps carry the same load whatever the
+// mix of context lengths; a span is cut into pieces at row ends.  The next piece starts at c.x and
+// takes at most `cap` tiles; returns false at the end of the span.  Piece number
+// x / span + row index is unique, below warps + rows, and consecutive within a row, which is how
+// the merge kernel finds a row's partials without any list.
+__device__ __forceinline__ bool next_piece(const DecodeParams &p, const int *s_cum, int span,
+                                           Cursor &c, int cap, Item &it) {
+  if (c.x >= c.end) return false;
+  const int H = p.num_kv_heads;
+  const int e = c.x / H;
+  int lo = 0, hi = p.num_seqs;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (s_cum[mid] <= e) lo = mid; else hi = mid;
+  }
+  const int c0 = s_cum[lo], tiles = s_cum[lo + 1] - c0;
+  const int rem = c.x - H * c0;
+  const int kvh = rem / tiles, t0 = rem - kvh * tiles;
+  int n = tiles - t0;
+  if (n > c.end - c.x) n = c.end - c.x;
+  if (n > cap) n = cap;
+  it.seq = lo;
+  it.chunk = 0;
+  it.kvh = kvh;
+  it.ctx = clamp_ctx(p, p.context_lens[lo]);
+  it.tok0 = t0 * kB;
+  it.ntiles = n;
+  const int g0 = c.x - t0;
+  it.single = (g0 + tiles - 1) / span == g0 / span;
+  it.pstep = 1;
+  it.pbase = (int64_t)(c.x / span + lo * H + kvh) * p.group;
+  c.x += n;
+  return true;
 }
 
 template <typename PartT>
@@ -116,7 +167,7 @@ __device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloat16 *dst, fl
   *reinterpret_cast<__nv_bfloat162 *>(dst) = __floats2bfloat162_rn(a, b);
 }
 
-template <typename PartT>
+template <typename PartT, bool kSpans>
 __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -163,6 +214,20 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
   const int n_items = n_entries * p.num_kv_heads;
   const int stride = gridDim.x * kWarps;
   const int gw = blockIdx.x * kWarps + warp;
+  // spans mode: n_items is the number of tiles of the whole batch (chunk_tokens == 16)
+  int span = 1;
+  Cursor p_cur = {0, 0}, c_cur = {0, 0};
+  if (kSpans) {
+    span = (n_items + stride - 1) / stride;
+    if (span < p.min_span) span = p.min_span;
+    const int64_t x0 = (int64_t)gw * span;
+    p_cur.x = c_cur.x = x0 < n_items ? (int)x0 : n_items;
+    p_cur.end = c_cur.end = x0 + span < n_items ? (int)(x0 + span) : n_items;
+    if (blockIdx.x == 0 && warp == 0) {  // what the merge kernel needs to find the pieces of a row
+      for (int i = lane; i <= p.num_seqs; i += 32) p.span_cum[i] = s_cum[i];
+      if (lane == 0) p.span_cum[p.num_seqs + 1] = span;
+    }
+  }
 
   // ---- producer cursor ---------------------------------------------------------------
   int p_idx = gw - stride;
@@ -176,14 +241,21 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
   auto produce_one = [&]() {
     if (p_done) return;
     if (p_tile == p_item.ntiles) {
-      do {
-        p_idx += stride;
-        if (p_idx >= n_items) {
+      if (kSpans) {
+        if (!next_piece(p, s_cum, span, p_cur, 32, p_item)) {  // 32 tiles: one block id per lane
           p_done = true;
           return;
         }
-        fetch_item(p, s_cum, p_idx, p_item);
-      } while (p_item.ntiles == 0);
+      } else {
+        do {
+          p_idx += stride;
+          if (p_idx >= n_items) {
+            p_done = true;
+            return;
+          }
+          fetch_item(p, s_cum, p_idx, p_item);
+        } while (p_item.ntiles == 0);
+      }
       int b = 0;
       if (lane < p_item.ntiles) {
         b = p.block_tables[(int64_t)p_item.seq * p.max_blocks_per_seq + p_item.tok0 / kB + lane];
@@ -225,12 +297,16 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
 
   while (!failed) {
     Item it;
-    do {
-      c_idx += stride;
+    if (kSpans) {
+      if (!next_piece(p, s_cum, span, c_cur, 0x7fffffff, it)) break;
+    } else {
+      do {
+        c_idx += stride;
+        if (c_idx >= n_items) break;
+        fetch_item(p, s_cum, c_idx, it);
+      } while (it.ntiles == 0);
       if (c_idx >= n_items) break;
-      fetch_item(p, s_cum, c_idx, it);
-    } while (it.ntiles == 0);
-    if (c_idx >= n_items) break;
+    }
 
     // query fragments: rows = heads of this kv head's group (rows >= group are zero)
     uint32_t qa[8][2];
@@ -329,8 +405,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
     if (g < p.group) {
       const int head = it.kvh * p.group + g;
       const float inv = __fdividef(1.f, l_run + 1e-6f);
-      const int n_chunks = (it.ctx + p.chunk_tokens - 1) / p.chunk_tokens;
-      if (n_chunks == 1) {
+      if (it.single) {
         const int64_t off = ((int64_t)it.seq * p.out_heads + p.out_head0 + head) * kD + 2 * tig;
         for (int w = 0; w < p.world; ++w) {
           __nv_bfloat16 *dst = p.out[w] + off;
@@ -339,8 +414,8 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
             store_pair<__nv_bfloat16>(dst + 8 * nt, o[nt][0] * inv, o[nt][1] * inv);
         }
       }
-      if (n_chunks > 1 || p.always_write_partials) {
-        const int64_t pidx = ((int64_t)it.seq * p.num_heads + head) * p.max_parts + it.chunk;
+      if (!it.single || p.always_write_partials) {
+        const int64_t pidx = it.pbase + (int64_t)g * it.pstep;
         if (tig == 0) {
           p.part_max[pidx] = m_run * kLn2;
           p.part_sum[pidx] = l_run;
@@ -359,74 +434,99 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
   }
 }
 
-// Combines the chunk partials of one (sequence, head): v2 reduce of the reference
-// (attention_kernels.cu:450-546).  One CTA of 8 warps per (sequence, head): every warp finds the
-// global maximum, then takes every 8th chunk -- one weight per lane, handed round by shuffle, so
-// the 512-byte row loads of a warp are independent -- and the eight partial sums meet in shared
-// memory.  Lane l owns d = 4l .. 4l+3.
+// Combines the partials of one (sequence, head): v2 reduce of the reference
+// (attention_kernels.cu:450-546).  A team of kTeam warps works on one row: every warp finds the
+// global maximum, then takes every kTeam-th partial -- one weight per lane, handed round by
+// shuffle, so the 512-byte row loads of a warp are independent -- and the team's sums meet in
+// shared memory.  Lane l owns d = 4l .. 4l+3.  kTeam = 8 (one row per CTA) suits rows with many
+// partials; kTeam = 1 (eight rows per CTA) suits the spans mode with large batches, where a row
+// has two or three.  In spans mode the partials of a row are consecutive pieces (see next_piece).
 constexpr int kMergeWarps = 8;
-template <typename PartT>
+template <typename PartT, bool kSpans, int kTeam>
 __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const DecodeParams p) {
   asm volatile("griddepcontrol.wait;" ::: "memory");  // no-op unless launched as a dependent grid
+  constexpr int kRows = kMergeWarps / kTeam;
   __shared__ float s_acc[kMergeWarps][kD];
   __shared__ float s_w[kMergeWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int seq = blockIdx.x / p.num_heads, head = blockIdx.x - seq * p.num_heads;
-  const int ctx = clamp_ctx(p, p.context_lens[seq]);
-  const int n = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
-  if (n == 1) return;  // the decode kernel wrote the row itself
-  const int64_t out_off = ((int64_t)seq * p.out_heads + p.out_head0 + head) * kD + 4 * lane;
-  if (n <= 0) {
-    if (warp == 0)
-      for (int w = 0; w < p.world; ++w) *reinterpret_cast<uint2 *>(p.out[w] + out_off) = make_uint2(0u, 0u);
-    return;
-  }
-  const int64_t base = ((int64_t)seq * p.num_heads + head) * p.max_parts;
-  float m = -INFINITY;
-  for (int j = lane; j < n; j += 32) m = fmaxf(m, p.part_max[base + j]);
-#pragma unroll
-  for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  float wsum = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-  const PartT *po = static_cast<const PartT *>(p.part_out) + base * kD + 4 * lane;
-  // this warp's chunks: warp, warp + 8, ...; lane l prepares the weight of chunk warp + 8 l
-  for (int j0 = warp; j0 < n; j0 += kMergeWarps * 32) {
-    const int cnt = min(32, (n - j0 + kMergeWarps - 1) / kMergeWarps);
-    float w_lane = 0.f;
-    if (lane < cnt) {
-      const int j = j0 + kMergeWarps * lane;
-      w_lane = p.part_sum[base + j] * __expf(p.part_max[base + j] - m);
+  const int team = warp / kTeam, tw = warp - team * kTeam;
+  const int row = blockIdx.x * kRows + team;
+  const bool active = row < p.num_seqs * p.num_heads;
+  const int seq = active ? row / p.num_heads : 0, head = active ? row - seq * p.num_heads : 0;
+  int n = 0, pstride = 1;
+  int64_t base = 0;
+  if (active) {
+    if (kSpans) {
+      const int c0 = p.span_cum[seq], tiles = p.span_cum[seq + 1] - c0;
+      const int span = p.span_cum[p.num_seqs + 1];
+      if (tiles > 0) {
+        const int kvh = head / p.group;
+        const int g0 = p.num_kv_heads * c0 + kvh * tiles;
+        const int first = g0 / span;
+        n = (g0 + tiles - 1) / span - first + 1;
+        base = (int64_t)(first + seq * p.num_kv_heads + kvh) * p.group + (head - kvh * p.group);
+        pstride = p.group;
+      }
+    } else {
+      const int ctx = clamp_ctx(p, p.context_lens[seq]);
+      n = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
+      base = (int64_t)row * p.max_parts;
     }
+  }
+  const int64_t out_off = ((int64_t)seq * p.out_heads + p.out_head0 + head) * kD + 4 * lane;
+  if (active && n <= 0 && tw == 0)  // empty context: the decode kernel never saw this row
+    for (int w = 0; w < p.world; ++w) *reinterpret_cast<uint2 *>(p.out[w] + out_off) = make_uint2(0u, 0u);
+  const bool work = active && n > 1;  // n == 1: the decode kernel wrote the row itself
+  float wsum = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  if (work) {
+    float m = -INFINITY;
+    for (int j = lane; j < n; j += 32) m = fmaxf(m, p.part_max[base + (int64_t)j * pstride]);
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const PartT *po = static_cast<const PartT *>(p.part_out) + base * kD + 4 * lane;
+    // this warp's partials: tw, tw + kTeam, ...; lane l prepares the weight of partial tw + kTeam l
+    for (int j0 = tw; j0 < n; j0 += kTeam * 32) {
+      const int cnt = min(32, (n - j0 + kTeam - 1) / kTeam);
+      float w_lane = 0.f;
+      if (lane < cnt) {
+        const int64_t j = base + (int64_t)(j0 + kTeam * lane) * pstride;
+        w_lane = p.part_sum[j] * __expf(p.part_max[j] - m);
+      }
 #pragma unroll 4
-    for (int l = 0; l < cnt; ++l) {
-      const float w = __shfl_sync(0xffffffffu, w_lane, l);
-      const int j = j0 + kMergeWarps * l;
-      wsum += w;
-      if (sizeof(PartT) == 4) {
-        const float4 v = *reinterpret_cast<const float4 *>(po + (int64_t)j * kD);
-        a0 += w * v.x; a1 += w * v.y; a2 += w * v.z; a3 += w * v.w;
-      } else {
-        const uint2 raw = *reinterpret_cast<const uint2 *>(po + (int64_t)j * kD);
-        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x);
-        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
-        a0 += w * __low2float(lo); a1 += w * __high2float(lo);
-        a2 += w * __low2float(hi); a3 += w * __high2float(hi);
+      for (int l = 0; l < cnt; ++l) {
+        const float w = __shfl_sync(0xffffffffu, w_lane, l);
+        const int64_t j = (int64_t)(j0 + kTeam * l) * pstride;
+        wsum += w;
+        if (sizeof(PartT) == 4) {
+          const float4 v = *reinterpret_cast<const float4 *>(po + j * kD);
+          a0 += w * v.x; a1 += w * v.y; a2 += w * v.z; a3 += w * v.w;
+        } else {
+          const uint2 raw = *reinterpret_cast<const uint2 *>(po + j * kD);
+          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x);
+          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
+          a0 += w * __low2float(lo); a1 += w * __high2float(lo);
+          a2 += w * __low2float(hi); a3 += w * __high2float(hi);
+        }
       }
     }
   }
-  *reinterpret_cast<float4 *>(&s_acc[warp][4 * lane]) = make_float4(a0, a1, a2, a3);
-  if (lane == 0) s_w[warp] = wsum;
-  __syncthreads();
-  if (warp == 0) {
-    float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f, tw = 0.f;
+  if (kTeam > 1) {
+    *reinterpret_cast<float4 *>(&s_acc[warp][4 * lane]) = make_float4(a0, a1, a2, a3);
+    if (lane == 0) s_w[warp] = wsum;
+    __syncthreads();
+    if (tw != 0) return;
+    a0 = a1 = a2 = a3 = wsum = 0.f;
 #pragma unroll
-    for (int w = 0; w < kMergeWarps; ++w) {
-      const float4 v = *reinterpret_cast<const float4 *>(&s_acc[w][4 * lane]);
-      t0 += v.x; t1 += v.y; t2 += v.z; t3 += v.w;
-      tw += s_w[w];
+    for (int w = 0; w < kTeam; ++w) {
+      const float4 v = *reinterpret_cast<const float4 *>(&s_acc[team * kTeam + w][4 * lane]);
+      a0 += v.x; a1 += v.y; a2 += v.z; a3 += v.w;
+      wsum += s_w[team * kTeam + w];
     }
-    const float inv = __fdividef(1.f, tw + 1e-6f);
-    const uint2 row = make_uint2(pack_bf16(t0 * inv, t1 * inv), pack_bf16(t2 * inv, t3 * inv));
-    for (int w = 0; w < p.world; ++w) *reinterpret_cast<uint2 *>(p.out[w] + out_off) = row;
+  }
+  if (work) {
+    const float inv = __fdividef(1.f, wsum + 1e-6f);
+    const uint2 packed = make_uint2(pack_bf16(a0 * inv, a1 * inv), pack_bf16(a2 * inv, a3 * inv));
+    for (int w = 0; w < p.world; ++w) *reinterpret_cast<uint2 *>(p.out[w] + out_off) = packed;
   }
 }
 
@@ -490,11 +590,12 @@ static int sm_count() {
   return cached[dev];
 }
 
-// Tokens per work item.  256 (16 cache blocks, 128 KB of K+V) keeps the partial-result traffic
-// near 1 %, but a warp streams only about 5 GB/s, so with few (sequence, kv head) pairs per GPU
-// -- heads sharded over many GPUs, or a small batch -- coarse items leave some warps with one
-// item more than others.  The chunk is halved until the upper bound of the item count reaches 16
-// per resident warp (about 8 real items for uniformly drawn contexts), down to 64 tokens.
+// Tokens per work item of the fixed-chunk traversal (used when the tuning hook asks for it, for
+// batches too large to plan inside the kernel, and -- with 512 -- for the v2 calling convention).
+// 256 (16 cache blocks, 128 KB of K+V) keeps the partial-result traffic near 1 %; with few
+// (sequence, kv head) pairs per GPU coarse items leave some warps with one item more than
+// others, so the chunk is halved until the upper bound of the item count reaches 16 per resident
+// warp, down to 64 tokens.
 static int pick_chunk(int num_seqs, int num_kv_heads, int max_context_len) {
   if (g_chunk_override > 0) return g_chunk_override;
   const int64_t warps = (int64_t)2 * sm_count() * kWarps;
@@ -503,6 +604,14 @@ static int pick_chunk(int num_seqs, int num_kv_heads, int max_context_len) {
          (int64_t)num_seqs * ((max_context_len + chunk - 1) / chunk) * num_kv_heads < 16 * warps)
     chunk >>= 1;
   return chunk;
+}
+
+// The default traversal gives every warp one span of consecutive tiles (see next_piece); it needs
+// the in-kernel plan, hence the batch limit, and 32-bit tile indices.
+constexpr int kMinSpanTiles = 4;
+static bool use_spans(int num_seqs, int num_kv_heads, int max_context_len) {
+  return g_chunk_override == 0 && num_seqs <= kMaxInlineSeqs &&
+         (int64_t)num_seqs * num_kv_heads * ((max_context_len + kB - 1) / kB + 1) < (1ll << 30);
 }
 
 constexpr size_t kAlign = 256;
@@ -524,6 +633,22 @@ static WorkspaceLayout workspace_layout(int num_seqs, int num_heads, int max_con
   w.sum_off = w.max_off + align_up(parts * num_heads * sizeof(float));
   w.out_off = w.sum_off + align_up(parts * num_heads * sizeof(float));
   w.total = w.out_off + align_up(parts * num_heads * kD * sizeof(float));
+  return w;
+}
+
+// Spans mode: tile prefix sums for the merge kernel, then one partial per piece and group head;
+// pieces are fewer than warps + rows whatever the context lengths are.
+static WorkspaceLayout spans_layout(int num_seqs, int num_heads, int num_kv_heads) {
+  WorkspaceLayout w;
+  const size_t pieces = (size_t)2 * sm_count() * kWarps + (size_t)num_seqs * num_kv_heads;
+  const size_t parts = pieces * (num_heads / num_kv_heads);
+  w.max_parts = 1;
+  w.n_entries_off = 0;
+  w.entries_off = kAlign;  // the prefix sums live where the chunk list would
+  w.max_off = w.entries_off + align_up((size_t)(num_seqs + 2) * sizeof(int));
+  w.sum_off = w.max_off + align_up(parts * sizeof(float));
+  w.out_off = w.sum_off + align_up(parts * sizeof(float));
+  w.total = w.out_off + align_up(parts * kD * sizeof(float));
   return w;
 }
 
@@ -562,7 +687,7 @@ static char *check_decode_args(const char *fn, const void *out, const void *quer
   return nullptr;
 }
 
-template <typename PartT>
+template <typename PartT, bool kSpans>
 static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaStream_t stream) {
   static bool attr_set[64] = {false};
   const int smem = kWarps * kStages * kStageBytes + kWarps * kStages * (int)sizeof(uint64_t) +
@@ -570,23 +695,32 @@ static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaS
   int dev = 0;
   AICI_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    AICI_CUDA(cudaFuncSetAttribute(paged_decode_kernel<PartT>,
+    AICI_CUDA(cudaFuncSetAttribute(paged_decode_kernel<PartT, kSpans>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[dev] = true;
   }
-  // small and medium batches: every CTA plans for itself; very large ones: a plan kernel writes
-  // the compact chunk list into the workspace (v2 convention, no workspace: virtual grid)
-  p.inline_plan = (entries != nullptr && p.num_seqs <= kMaxInlineSeqs) ? 1 : 0;
-  if (entries != nullptr && !p.inline_plan) {
-    paged_plan_kernel<<<1, 1024, 0, stream>>>(p, entries, n_entries);
-    AICI_CUDA(cudaGetLastError());
-  }
-  p.entries = p.inline_plan ? nullptr : entries;
-  p.n_entries = n_entries;
-  const int64_t ub_items = (int64_t)p.num_seqs * p.max_parts * p.num_kv_heads;
   int grid = 2 * sm_count();
-  const int64_t need = (ub_items + kWarps - 1) / kWarps;
-  if (need < grid) grid = (int)need;
+  if (kSpans) {
+    p.inline_plan = 1;
+    p.entries = nullptr;
+    p.n_entries = nullptr;
+    const int64_t ub_tiles = (int64_t)p.num_seqs * p.num_kv_heads * ((p.max_context_len + kB - 1) / kB);
+    const int64_t need = (ub_tiles + (int64_t)kWarps * kMinSpanTiles - 1) / (kWarps * kMinSpanTiles);
+    if (need < grid) grid = (int)need;
+  } else {
+    // small and medium batches: every CTA plans for itself; very large ones: a plan kernel writes
+    // the compact chunk list into the workspace (v2 convention, no workspace: virtual grid)
+    p.inline_plan = (entries != nullptr && p.num_seqs <= kMaxInlineSeqs) ? 1 : 0;
+    if (entries != nullptr && !p.inline_plan) {
+      paged_plan_kernel<<<1, 1024, 0, stream>>>(p, entries, n_entries);
+      AICI_CUDA(cudaGetLastError());
+    }
+    p.entries = p.inline_plan ? nullptr : entries;
+    p.n_entries = n_entries;
+    const int64_t ub_items = (int64_t)p.num_seqs * p.max_parts * p.num_kv_heads;
+    const int64_t need = (ub_items + kWarps - 1) / kWarps;
+    if (need < grid) grid = (int)need;
+  }
   if (grid < 1) grid = 1;
   // decode and merge are launched as programmatic dependents: their prologues overlap the tail of
   // the grid before them, and each waits (griddepcontrol.wait) before touching its inputs
@@ -600,11 +734,19 @@ static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaS
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kWarps * 32);
   cfg.dynamicSmemBytes = smem;
-  AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_decode_kernel<PartT>, p));
-  cfg.gridDim = dim3(p.num_seqs * p.num_heads);
+  AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_decode_kernel<PartT, kSpans>, p));
   cfg.blockDim = dim3(kMergeWarps * 32);
   cfg.dynamicSmemBytes = 0;
-  AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_merge_kernel<PartT>, p));
+  const int rows = p.num_seqs * p.num_heads;
+  // many (sequence, kv head) rows per warp of the decode grid: a row has few partials, one warp
+  // merges it; few rows: a row has many partials, eight warps share it
+  if (kSpans && (int64_t)p.num_seqs * p.num_kv_heads * 4 >= (int64_t)grid * kWarps) {
+    cfg.gridDim = dim3((rows + kMergeWarps - 1) / kMergeWarps);
+    AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_merge_kernel<PartT, kSpans, 1>, p));
+  } else {
+    cfg.gridDim = dim3(rows);
+    AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_merge_kernel<PartT, kSpans, kMergeWarps>, p));
+  }
   return nullptr;
 }
 
@@ -624,6 +766,8 @@ extern "C" char *aici_tune_decode_chunk(int chunk_tokens) {
 extern "C" size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads, int num_kv_heads,
                                                        int max_context_len) {
   if (num_seqs <= 0 || num_heads <= 0 || num_kv_heads <= 0) return kAlign;
+  if (use_spans(num_seqs, num_kv_heads, max_context_len))
+    return spans_layout(num_seqs, num_heads, num_kv_heads).total;
   return workspace_layout(num_seqs, num_heads, max_context_len,
                           pick_chunk(num_seqs, num_kv_heads, max_context_len)).total;
 }
@@ -648,8 +792,10 @@ static char *paged_attention_v1_impl(const char *fn, void *const *outs, int worl
                                   kv_head_stride, dtype))
     return e;
   if (num_seqs == 0) return nullptr;
-  const int chunk = pick_chunk(num_seqs, num_kv_heads, max_context_len);
-  const WorkspaceLayout w = workspace_layout(num_seqs, num_heads, max_context_len, chunk);
+  const bool spans = use_spans(num_seqs, num_kv_heads, max_context_len);
+  const int chunk = spans ? kB : pick_chunk(num_seqs, num_kv_heads, max_context_len);
+  const WorkspaceLayout w = spans ? spans_layout(num_seqs, num_heads, num_kv_heads)
+                                  : workspace_layout(num_seqs, num_heads, max_context_len, chunk);
   AICI_CHECK(workspace != nullptr && workspace_bytes >= w.total,
              "%s: workspace too small (%zu bytes given, %zu needed)", fn, workspace_bytes, w.total);
   AICI_CHECK((uintptr_t)workspace % kAlign == 0, "%s: workspace must be 256-byte aligned", fn);
@@ -679,14 +825,17 @@ static char *paged_attention_v1_impl(const char *fn, void *const *outs, int worl
   p.chunk_tokens = chunk;
   p.max_parts = w.max_parts;
   p.always_write_partials = 0;
+  p.span_cum = reinterpret_cast<int *>(ws + w.entries_off);
+  p.min_span = kMinSpanTiles;
   p.q_stride = q_stride;
   p.kv_block_stride = kv_block_stride;
   p.kv_head_stride = kv_head_stride;
   p.scale_log2e = scale * kLog2e;
   p.status = st;
-  return launch_decode<float>(p, reinterpret_cast<int2 *>(ws + w.entries_off),
-                              reinterpret_cast<int *>(ws + w.n_entries_off),
-                              static_cast<cudaStream_t>(stream));
+  if (spans) return launch_decode<float, true>(p, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+  return launch_decode<float, false>(p, reinterpret_cast<int2 *>(ws + w.entries_off),
+                                     reinterpret_cast<int *>(ws + w.n_entries_off),
+                                     static_cast<cudaStream_t>(stream));
 }
 
 extern "C" char *aici_paged_attention_v1(void *out, const void *query, const void *key_cache,
@@ -778,12 +927,14 @@ extern "C" char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_
   p.chunk_tokens = 512;  // PARTITION_SIZE of the reference
   p.max_parts = max_context_len > 0 ? (max_context_len + 511) / 512 : 1;
   p.always_write_partials = 1;
+  p.span_cum = nullptr;
+  p.min_span = 1;
   p.q_stride = q_stride;
   p.kv_block_stride = kv_block_stride;
   p.kv_head_stride = kv_head_stride;
   p.scale_log2e = scale * kLog2e;
   p.status = st;
-  return launch_decode<__nv_bfloat16>(p, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+  return launch_decode<__nv_bfloat16, false>(p, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 // ---- decode attention for callers that cannot provide scratch memory ------------------------------
@@ -799,14 +950,14 @@ extern "C" char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_
 // Rules that follow from sharing one array:
 //   * sizes whose workspace would exceed kStaticScratchBytes are refused with an error string;
 //   * the array keeps whatever the previous call left; nothing in it has to start at zero (the
-//     plan kernel writes the chunk count and list, every partial is written before it is read),
-//     so no clearing pass runs;
+//     decode kernel writes the prefix sums or the chunk list, every partial is written before it
+//     is read), so no clearing pass runs;
 //   * two calls that overlap on the GPU (different streams, or different threads on one device)
 //     race on the array -- serialise them on one stream;
 //   * the first call on each device looks the array's device address up (the name used in host
 //     code is only a handle, not an address a kernel could use) and sets a function attribute;
 //     make that first call outside any stream capture.
-constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB: config 2 (64 x 32 heads x 4096 ctx) needs 17 MiB
+constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB: 256 sequences x 32/8 heads need 7 MiB, 2048 x 32/8 do not fit
 static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
 
 extern "C" char *aici_paged_attention_v1_static(
@@ -831,7 +982,7 @@ extern "C" char *aici_paged_attention_v1_static(
         aici_paged_attention_workspace_bytes(num_seqs, num_heads, num_kv_heads, max_context_len);
     AICI_CHECK(need <= kStaticScratchBytes,
                "%s: this batch needs %zu bytes of scratch but the built-in array holds %zu "
-               "(num_seqs * ceil(max_context_len / chunk) * num_heads is too large); use "
+               "(about 520 bytes per query head and (warp of the grid + sequence x kv head)); use "
                "aici_paged_attention_v1 with a caller-owned workspace",
                fn, need, kStaticScratchBytes);
   }

@@ -82,6 +82,48 @@ def test_large_batch_uses_the_plan_kernel(cuda_device):
     assert _lib.last_status() == 0
 
 
+@pytest.mark.parametrize("hq,hkv,ctx", [
+    (8, 1, [8000]),                       # one row cut into many pieces: eight warps merge it
+    (4, 4, [3000, 0, 0, 1]),              # empty contexts between rows
+    (8, 8, [16] * 40 + [5000] + [1] * 30),  # many one-tile rows around a long one
+    (32, 8, [37] * 300),                  # more rows than warps: most spans hold several rows
+    (8, 2, [0, 0, 0]),                    # nothing to read at all
+])
+def test_span_traversal_shapes(cuda_device, hq, hkv, ctx):
+    """The default traversal gives each warp one span of consecutive tiles of the whole batch;
+    these batches put the span borders in every position relative to the row borders."""
+    nblk = sum((c + 15) // 16 for c in ctx) + 4
+    q, kc, vc, bt, cl = _case(360 + len(ctx), hq, hkv, ctx, nblk)
+    want = O.paged_attention_v1(q, kc, vc, hkv, 0.088, bt, cl)
+    out = torch.full(q.shape, float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    tch_cuda.paged_attention_v1(out, q.to(cuda_device), kc.to(cuda_device), vc.to(cuda_device), hkv,
+                                0.088, bt.to(cuda_device), cl.to(cuda_device), 16, max(max(ctx), 1), None)
+    got = out.cpu()
+    _check(got, want)
+    for i, c in enumerate(ctx):
+        if c == 0:
+            assert float(got[i].float().abs().max()) == 0.0
+    assert _lib.last_status() == 0
+
+
+def test_span_and_chunk_traversals_agree(cuda_device):
+    """Same batch through both traversals (the tuning hook selects the fixed-chunk one)."""
+    w = workloads.make_decode("t", cuda_device, num_seqs=48, num_heads=32, num_kv_heads=8,
+                              ctx_kind="loguniform", ctx_lo=16, ctx_hi=4000, pool_blocks=8192, seed=365)
+    a, b = torch.empty_like(w.query), torch.empty_like(w.query)
+    tch_cuda.paged_attention_v1(a, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                w.block_tables, w.context_lens, 16, w.max_context_len, None)
+    _lib.check("tune", _lib.lib().aici_tune_decode_chunk(256))
+    try:
+        tch_cuda.paged_attention_v1(b, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                    w.block_tables, w.context_lens, 16, w.max_context_len, None)
+    finally:
+        _lib.check("tune", _lib.lib().aici_tune_decode_chunk(0))
+    d = (a.float() - b.float()).abs()
+    assert float(d.max()) <= 4e-3, float(d.max())  # same tiles, different split points
+    assert _lib.last_status() == 0
+
+
 @pytest.mark.parametrize("chunk", [16, 64, 512])
 def test_chunk_sizes(cuda_device, chunk):
     ctx = [700, 16, 1, 2049, 130]

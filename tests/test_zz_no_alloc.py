@@ -44,14 +44,14 @@ def test_static_scratch_entry_point_matches_twice_in_a_row(cuda_device):
 
 
 def test_static_scratch_entry_point_refuses_oversized_batches(cuda_device):
-    need = _lib.lib().aici_paged_attention_workspace_bytes(ctypes.c_int(256), ctypes.c_int(32),
+    need = _lib.lib().aici_paged_attention_workspace_bytes(ctypes.c_int(2048), ctypes.c_int(32),
                                                            ctypes.c_int(8), ctypes.c_int(8192))
     assert need > (32 << 20)
     w = workloads.make_decode("c", cuda_device, num_seqs=2, num_heads=8, num_kv_heads=8,
                               ctx_kind="uniform", ctx_lo=20, ctx_hi=40, pool_blocks=16, seed=912)
-    q = w.query[:1].expand(256, 8, 128).contiguous().repeat(1, 4, 1)  # 256 seqs x 32 heads
-    bt = w.block_tables[:1].expand(256, -1).contiguous()
-    cl = w.context_lens[:1].expand(256).contiguous()
+    q = w.query[:1].expand(2048, 8, 128).contiguous().repeat(1, 4, 1)  # 2048 seqs x 32 heads
+    bt = w.block_tables[:1].expand(2048, -1).contiguous()
+    cl = w.context_lens[:1].expand(2048).contiguous()
     out = torch.empty_like(q)
     with pytest.raises(_lib.AiciError, match="built-in array holds"):
         tch_cuda.paged_attention_v1_static(out, q, w.key_cache, w.value_cache, 8, w.scale, bt, cl, 16,
