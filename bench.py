@@ -41,7 +41,7 @@ CPU_SAMPLE_SEQS = 8
 # DRAM bytes (read + write) of paged_decode_kernel per algorithmic byte, from an ncu capture of
 # the 16-sequence case that `--profile decode` runs; traffic grows in proportion to the tokens
 # read, so the ratio carries over to the full launch.
-DECODE_TRAFFIC_RATIO = 1.025
+DECODE_TRAFFIC_RATIO = 1.011
 
 
 def load_peaks():
