@@ -188,24 +188,28 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
   asm volatile("griddepcontrol.wait;" ::: "memory");
   int *s_cum = reinterpret_cast<int *>(smem + kWarps * kStages * kStageBytes + kWarps * kStages * sizeof(uint64_t));
   if (p.inline_plan) {
-    // chunk-count prefix sums over the batch, built by warp 0 of every CTA
+    // chunk-count prefix sums over the batch, built by every CTA for itself: all threads fetch
+    // the context lengths at once (one global-memory latency for the whole batch), then warp 0
+    // scans the counts in shared memory
+    for (int seq = threadIdx.x; seq < p.num_seqs; seq += kWarps * 32)
+      s_cum[seq + 1] = (clamp_ctx(p, p.context_lens[seq]) + p.chunk_tokens - 1) / p.chunk_tokens;
+    __syncthreads();
     if (warp == 0) {
       int carry = 0;
       for (int s0 = 0; s0 < p.num_seqs; s0 += 32) {
         const int seq = s0 + lane;
-        int cnt = 0;
-        if (seq < p.num_seqs)
-          cnt = (clamp_ctx(p, p.context_lens[seq]) + p.chunk_tokens - 1) / p.chunk_tokens;
+        const int cnt = seq < p.num_seqs ? s_cum[seq + 1] : 0;
         int incl = cnt;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
           const int v = __shfl_up_sync(0xffffffffu, incl, o);
           if (lane >= o) incl += v;
         }
-        if (seq < p.num_seqs) s_cum[seq] = carry + incl - cnt;
+        __syncwarp();
+        if (seq < p.num_seqs) s_cum[seq + 1] = carry + incl;
         carry += __shfl_sync(0xffffffffu, incl, 31);
       }
-      if (lane == 0) s_cum[p.num_seqs] = carry;
+      if (lane == 0) s_cum[0] = 0;
     }
     __syncthreads();
   }
