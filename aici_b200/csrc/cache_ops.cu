@@ -22,6 +22,47 @@ __device__ __forceinline__ int64_t load_slot(const void *slots, int64_t i) {
   return static_cast<int64_t>(static_cast<const int32_t *>(slots)[i]);
 }
 
+// Writes the CTA's staged value tile s_v[tok][d] (16 tokens x 128) to the cache.
+__device__ __forceinline__ void store_value_tile(const int64_t *s_slot,
+                                                 const __nv_bfloat16 (*s_v)[kD + 8],
+                                                 __nv_bfloat16 *__restrict__ value_cache,
+                                                 int num_kv_heads, int h, int tid) {
+  // aligned: both 8-token halves are runs of consecutive slots starting at a multiple of 8 (the
+  // prefill case: a sequence's tokens fill whole cache blocks in order)
+  bool aligned = true;
+#pragma unroll
+  for (int tb = 0; tb < kTok; tb += 8) {
+    const int64_t s0 = s_slot[tb];
+    aligned = aligned && s0 >= 0 && (s0 % 8) == 0;
+#pragma unroll
+    for (int j = 1; j < 8; ++j) aligned = aligned && (s_slot[tb + j] == s0 + j);
+  }
+  if (aligned) {
+    // a warp covers 32 consecutive d of one token half: column reads hit 16 distinct banks
+    const int d = tid & (kD - 1), half = tid >> 7;
+    const int tb = half * 8;
+    const int64_t s0 = s_slot[tb];
+    uint4 val;
+    __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&val);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] = s_v[tb + j][d];
+    const int64_t blk = s0 / kB, off = s0 % kB;
+    *reinterpret_cast<uint4 *>(value_cache + ((blk * num_kv_heads + h) * kD + d) * kB + off) = val;
+  } else {
+    // any slots (decode steps, chunks that start in the middle of a block, skipped tokens):
+    // 16 consecutive threads take the 16 tokens of one d, so tokens with consecutive slots
+    // still land in one 32-byte sector per store instruction
+    const int tok = tid & (kTok - 1);
+    const int64_t slot = s_slot[tok];
+    if (slot >= 0) {
+      const int64_t blk = slot / kB, off = slot % kB;
+      __nv_bfloat16 *dst = value_cache + (blk * num_kv_heads + h) * (int64_t)(kD * kB) + off;
+#pragma unroll
+      for (int d = tid >> 4; d < kD; d += kThreads / kTok) dst[(int64_t)d * kB] = s_v[tok][d];
+    }
+  }
+}
+
 // One CTA moves kTok consecutive tokens of one kv head.
 //   K: chunk c (8 elements) of token t -> key_cache[blk][h][c][off][0..7]   (16 B vector)
 //   V: element d of token t            -> value_cache[blk][h][d][off]       (2 B, 32 B apart)
@@ -77,32 +118,7 @@ reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
           value + (int64_t)(t0 + tok) * value_stride + h * kD + part * kX);
   }
   __syncthreads();
-  {
-    // a warp covers 32 consecutive d of one token half: column reads hit 16 distinct banks
-    const int d = tid & (kD - 1), half = tid >> 7;
-    const int tb = half * 8;
-    const int64_t s0 = s_slot[tb];
-    bool run = s0 >= 0 && (s0 % 8) == 0;
-#pragma unroll
-    for (int j = 1; j < 8; ++j) run = run && (s_slot[tb + j] == s0 + j);
-    if (run) {
-      uint4 val;
-      __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&val);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) e[j] = s_v[tb + j][d];
-      const int64_t blk = s0 / kB, off = s0 % kB;
-      *reinterpret_cast<uint4 *>(value_cache + ((blk * num_kv_heads + h) * kD + d) * kB + off) = val;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int64_t slot = s_slot[tb + j];
-        if (slot >= 0) {
-          const int64_t blk = slot / kB, off = slot % kB;
-          value_cache[((blk * num_kv_heads + h) * kD + d) * kB + off] = s_v[tb + j][d];
-        }
-      }
-    }
-  }
+  store_value_tile(s_slot, s_v, value_cache, num_kv_heads, h, tid);
 }
 
 // Inverse traversal: cache -> packed key/value rows.
@@ -504,31 +520,7 @@ rotary_reshape_and_cache_kernel(const int64_t *__restrict__ positions, __nv_bflo
     }
   }
   __syncthreads();
-  {
-    const int d = tid & (kD - 1), half = tid >> 7;
-    const int tb = half * 8;
-    const int64_t s0 = s_slot[tb];
-    bool run = s0 >= 0 && (s0 % 8) == 0;
-#pragma unroll
-    for (int j = 1; j < 8; ++j) run = run && (s_slot[tb + j] == s0 + j);
-    if (run) {
-      uint4 val;
-      __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&val);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) e[j] = s_v[tb + j][d];
-      const int64_t blk = s0 / kB, off = s0 % kB;
-      *reinterpret_cast<uint4 *>(value_cache + ((blk * num_kv_heads + h) * kD + d) * kB + off) = val;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int64_t slot = s_slot[tb + j];
-        if (slot >= 0) {
-          const int64_t blk = slot / kB, off = slot % kB;
-          value_cache[((blk * num_kv_heads + h) * kD + d) * kB + off] = s_v[tb + j][d];
-        }
-      }
-    }
-  }
+  store_value_tile(s_slot, s_v, value_cache, num_kv_heads, h, tid);
 }
 
 }  // namespace aici

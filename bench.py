@@ -572,7 +572,10 @@ def run_suite(args):
     kk = torch.cat([pw.k, pw.k[:192]]).contiguous()
     slots = torch.arange(4288, dtype=torch.int32, device=dev) + 5
     r_ms, _ = timed(lambda: tch_cuda.reshape_and_cache(kk, kk, kc, vc, slots))
-    add("5-reshape_and_cache 4288 tokens", "hbm", 4288 * hkv * 128 * 2 * 2 * 2, r_ms, 0.0)
+    add("5-reshape_and_cache 4288 tokens, chunks starting mid-block", "hbm", 4288 * hkv * 128 * 2 * 2 * 2, r_ms, 0.0)
+    slots_a = torch.arange(4288, dtype=torch.int32, device=dev)
+    r_ms, _ = timed(lambda: tch_cuda.reshape_and_cache(kk, kk, kc, vc, slots_a))
+    add("5-reshape_and_cache 4288 tokens, block-aligned chunks", "hbm", 4288 * hkv * 128 * 2 * 2 * 2, r_ms, 0.0)
     del pw, buf, kc, vc, kk
 
     # prefill from the paged cache (the "next" row): the same long-context problem with K/V living

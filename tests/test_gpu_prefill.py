@@ -134,6 +134,32 @@ def test_long_context_sampled_rows(cuda_device):
     assert mx <= MAX_ABS and mean <= MEAN_ABS, (mx, mean)
 
 
+def test_config4_full_size_sampled_rows(cuda_device):
+    """Config 4 at full size (2 x 32768, 64 q / 8 kv heads, 35 TFLOP): the CPU cannot evaluate it
+    whole, so it checks, row by row in fp32, every row of the first and last query tile of each
+    sequence for four heads (two kv groups) plus 4096 random (sequence, row, head) triples."""
+    L = 32768
+    w = workloads.prefill_long(cuda_device)
+    assert w.q.shape[0] == 2 * L
+    out = _run(cuda_device, w)
+    torch.cuda.synchronize()
+    assert _lib.last_status() == 0
+    g = torch.Generator().manual_seed(82)
+    rows = []
+    for s in range(2):
+        for h in (0, 7, 8, 63):
+            rows += [[s, s * L + r, h] for r in list(range(128)) + list(range(L - 128, L))]
+    rnd_tok = torch.randint(0, 2 * L, (4096,), generator=g)
+    rnd_head = torch.randint(0, 64, (4096,), generator=g)
+    rows += [[int(t) // L, int(t), int(h)] for t, h in zip(rnd_tok, rnd_head)]
+    rows = torch.tensor(rows, dtype=torch.int32)
+    want = O.flash_attn_varlen_rows(w.q.cpu(), w.k.cpu(), w.v.cpu(), w.cu_seqlens_q.cpu(),
+                                    w.cu_seqlens_k.cpu(), rows, w.scale, True)
+    got = out[rows[:, 1].long().to(cuda_device), rows[:, 2].long().to(cuda_device)].cpu()
+    mx, mean = O.error_stats(got, want)
+    assert mx <= MAX_ABS and mean <= MEAN_ABS, (mx, mean)
+
+
 def test_rejects_unsupported(cuda_device):
     q = torch.zeros(4, 2, 64, dtype=torch.bfloat16, device=cuda_device)
     cu = torch.tensor([0, 4], dtype=torch.int32, device=cuda_device)
