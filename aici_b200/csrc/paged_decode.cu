@@ -5,19 +5,24 @@
 // t < context_len, softmax with the reference's +1e-6 in the denominator, fp32 accumulation
 // of p*V, kv head = head / (num_heads / num_kv_heads).
 //
-// The traversal is new.  The unit of work is one (sequence, kv head, chunk of the context);
-// every warp is an independent streaming agent:
+// The traversal is new.  Every warp is an independent streaming agent that works through a list of
+// pieces, a piece being some consecutive 16-token tiles of one (sequence, kv head) row:
 //   * lane 0 issues 1-D bulk copies (cp.async.bulk, completion on an mbarrier) that bring
 //     the 4 KB key tile and the 4 KB value tile of one 16-token cache block into the warp's
-//     private shared-memory ring, kStages deep, running ahead across work items;
+//     private shared-memory ring, kStages deep, running ahead across pieces;
 //   * the warp multiplies the whole query-head group of that kv head against the tile with
 //     bf16 mma.sync (q heads are the M rows, padded to 16), keeps an online softmax per row
 //     in registers (warp shuffles for the row max/sum), and accumulates P*V in fp32;
-//   * at the end of a chunk it writes either the final row (single-chunk sequences) or an
+//   * at the end of a piece it writes either the final row (the row had no other piece) or an
 //     fp32 partial (max, sum, normalised output) that a merge kernel combines.
 // So K/V are read from HBM exactly once per (sequence, kv head) regardless of the group
-// size, every byte moves as a 4 KB contiguous burst, and long contexts are split so that
-// all warps of all SMs carry the same amount of work.
+// size and every byte moves as a 4 KB contiguous burst.
+// Two ways of cutting the batch into pieces exist.  "Spans" (the default of the v1 entry): the
+// tiles of the whole batch are laid end to end and every warp of the grid takes one run of the
+// same length, so the load is even whatever the context lengths are (next_piece).  "Chunks": every
+// row is cut into chunks of a fixed number of tokens that are dealt out round-robin (fetch_item);
+// kept for the v2 calling convention, whose 512-token partitions are part of its output, for
+// batches too large to plan inside the kernel, and behind the tuning hook.
 #include "common.cuh"
 
 namespace aici {
