@@ -22,6 +22,28 @@ _DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 _workspaces: Dict[tuple, torch.Tensor] = {}
 
 
+class _on_device:
+    """Makes `dev` the current CUDA device for the duration of a call; does nothing (and costs
+    next to nothing) when it already is, which is the case on every call of a one-GPU process."""
+    __slots__ = ("index", "prev")
+
+    def __init__(self, dev: torch.device):
+        self.index = dev.index if dev.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.index:
+            self.prev = cur
+            torch.cuda.set_device(self.index)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
 def _p(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
@@ -92,7 +114,7 @@ def flash_attn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seqlens
     if tuple(v.shape) != tuple(k.shape) or k.shape[2] != head_size:
         raise AiciError("%s: k and v must be [total_k, num_heads_k, head_size]" % fn)
     out = torch.empty((total_q, num_heads, head_size), dtype=q.dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         res = _lib.lib().aici_mha_varlen_fwd(
             _p(out), _p(q), _p(k), _p(v), _p(seqlens_q), _p(seqlens_k), ctypes.c_int(batch),
             ctypes.c_int(total_q), ctypes.c_int(total_k), ctypes.c_int(num_heads),
@@ -133,7 +155,7 @@ def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.T
         raise AiciError("%s: slot_mapping must have one entry per token" % fn)
     if key_cache.dtype != key.dtype or value_cache.dtype != key.dtype:
         raise AiciError("%s: cache dtype differs from key dtype" % fn)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         res = _lib.lib().aici_reshape_and_cache(
             _p(key), _p(value), _p(key_cache), _p(value_cache), _p(slot_mapping),
             ctypes.c_int(1 if slot_mapping.dtype == torch.int64 else 0),
@@ -160,7 +182,7 @@ def gather_cached_kv(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Te
         raise AiciError("%s: slot_mapping must be contiguous int32" % fn)
     if slot_mapping.numel() != key.shape[0]:
         raise AiciError("%s: slot_mapping must have one entry per token" % fn)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         res = _lib.lib().aici_gather_cached_kv(
             _p(key), _p(value), _p(key_cache), _p(value_cache), _p(slot_mapping),
             ctypes.c_int(key.shape[0]), ctypes.c_int(num_kv_heads), ctypes.c_int(head_size),
@@ -209,7 +231,7 @@ def copy_blocks(key_caches: Sequence[torch.Tensor], value_caches: Sequence[torch
     kp = (ctypes.c_int64 * num_layers)(*[t.data_ptr() for t in key_caches])
     vp = (ctypes.c_int64 * num_layers)(*[t.data_ptr() for t in value_caches])
     mp = ctypes.c_void_p(flat.data_ptr())
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         res = _lib.lib().aici_copy_blocks_host(
             kp, vp, mp, ctypes.c_int(num_layers), ctypes.c_int(num_pairs),
             ctypes.c_int64(numel_per_block), ctypes.c_int64(num_blocks),
@@ -228,7 +250,7 @@ def copy_blocks_2(key_cache_ptrs_tensor: torch.Tensor, value_cache_ptrs_tensor: 
             raise AiciError("%s: pointer and mapping tensors must be contiguous int64" % fn)
     num_layers = key_cache_ptrs_tensor.numel()
     num_pairs = block_mapping_tensor.numel() // 2
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         res = _lib.lib().aici_copy_blocks(
             _p(key_cache_ptrs_tensor), _p(value_cache_ptrs_tensor), _p(block_mapping_tensor),
             ctypes.c_int(num_layers), ctypes.c_int(num_pairs), ctypes.c_int64(key0[0].numel()),
@@ -266,7 +288,7 @@ def swap_blocks(src: torch.Tensor, dst: torch.Tensor, block_mapping) -> None:
         return
     dev = cuda[0].device
     block_bytes = src[0].numel() * src.element_size()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _lib.check(fn, _lib.lib().aici_swap_blocks(
             _p(src), _p(dst), ctypes.c_void_p(pairs.data_ptr()), ctypes.c_int(pairs.numel() // 2),
             ctypes.c_int64(block_bytes), ctypes.c_int64(src.shape[0]), ctypes.c_int64(dst.shape[0]),
@@ -323,7 +345,7 @@ def paged_attention_v1(out: torch.Tensor, query: torch.Tensor, key_cache: torch.
                                                 num_kv_heads, block_tables, context_lens, block_size)
     num_seqs, num_heads, _ = query.shape
     L = _lib.lib()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         nbytes = L.aici_paged_attention_workspace_bytes(
             ctypes.c_int(num_seqs), ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads),
             ctypes.c_int(int(max_context_len)))
@@ -365,7 +387,7 @@ def paged_attention_v2(out: torch.Tensor, exp_sums: torch.Tensor, max_logits: to
         raise AiciError("%s: temporaries must be contiguous" % fn)
     if tmp_out.dtype != query.dtype:
         raise AiciError("%s: tmp_out dtype differs from query" % fn)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         res = _lib.lib().aici_paged_attention_v2(
             _p(out), _p(exp_sums), _p(max_logits), _p(tmp_out), _p(query), _p(key_cache),
             _p(value_cache), ctypes.c_int(num_kv_heads), ctypes.c_float(scale), _p(block_tables),
@@ -390,7 +412,7 @@ def paged_attention_v1_static(out: torch.Tensor, query: torch.Tensor, key_cache:
     dev, num_blocks, head_size = _decode_common(fn, out, query, key_cache, value_cache,
                                                 num_kv_heads, block_tables, context_lens, block_size)
     num_seqs, num_heads, _ = query.shape
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         res = _lib.lib().aici_paged_attention_v1_static(
             _p(out), _p(query), _p(key_cache), _p(value_cache), ctypes.c_int(num_kv_heads),
             ctypes.c_float(scale), _p(block_tables), _p(context_lens), ctypes.c_int(block_size),
@@ -428,7 +450,7 @@ def flash_attn_varlen_paged(q: torch.Tensor, key_cache: torch.Tensor, value_cach
         raise AiciError("%s: query and cache dtypes differ" % fn)
     total_q, num_heads, _ = q.shape
     out = torch.empty((total_q, num_heads, head_size), dtype=q.dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         res = _lib.lib().aici_mha_varlen_paged_fwd(
             _p(out), _p(q), _p(key_cache), _p(value_cache), _p(seqlens_q), _p(context_lens),
             _p(block_tables), ctypes.c_int(batch), ctypes.c_int(total_q), ctypes.c_int(num_heads),
@@ -469,7 +491,7 @@ def rotary_embedding_reshape_and_cache(positions: torch.Tensor, query: torch.Ten
         raise AiciError("%s: slot_mapping must be contiguous int32 or int64 [num_tokens]" % fn)
     if cos_sin_cache.dim() != 2 or not cos_sin_cache.is_contiguous() or cos_sin_cache.dtype != query.dtype:
         raise AiciError("%s: cos_sin_cache must be contiguous [max_position, rot_dim] of the query dtype" % fn)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         res = _lib.lib().aici_rotary_reshape_and_cache(
             _p(positions), _p(query), _p(key), _p(value), _p(cos_sin_cache), _p(key_cache), _p(value_cache),
             _p(slot_mapping), ctypes.c_int(1 if slot_mapping.dtype == torch.int64 else 0), ctypes.c_int(T),
@@ -503,7 +525,7 @@ def paged_attention_v1_peers(peer_ptrs: Sequence[int], total_heads: int, head0: 
     world = len(peer_ptrs)
     outs = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in peer_ptrs])
     L = _lib.lib()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         nbytes = L.aici_paged_attention_workspace_bytes(
             ctypes.c_int(num_seqs), ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads),
             ctypes.c_int(int(max_context_len)))
@@ -536,7 +558,7 @@ def flash_attn_varlen_peers(peer_ptrs: Sequence[int], total_heads: int, head0: i
     batch = seqlens_q.numel() - 1
     world = len(peer_ptrs)
     outs = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in peer_ptrs])
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         res = _lib.lib().aici_mha_varlen_fwd_peers(
             outs, ctypes.c_int(world), ctypes.c_int(head0), _p(q), _p(k), _p(v), _p(seqlens_q), _p(seqlens_k),
             ctypes.c_int(batch), ctypes.c_int(total_q), ctypes.c_int(k.shape[0]), ctypes.c_int(num_heads),
