@@ -447,6 +447,74 @@ inline void paged_attention_v2(Tensor &out, Tensor &exp_sums, Tensor &max_logits
                                     detail::dtype_of(fn, query), stream));
 }
 
+// Additions that have no function of their own in the crate --------------------------------------
+
+// Prefill attention with keys/values read from the paged cache through block tables: what
+// compute_varlen_attn (rllm-cuda/src/llm/mod.rs:168-278) gets from gather_cached_kv + repeat_kv +
+// flash_attn_varlen, without the gathered copy.  seqlens_q cumulative int32 [batch + 1];
+// context_lens int32 [batch]; block_tables int32 [batch, max_blocks].
+inline Tensor flash_attn_varlen_paged(const Tensor &q, const Tensor &key_cache, const Tensor &value_cache,
+                                      const Tensor &seqlens_q, const Tensor &context_lens,
+                                      const Tensor &block_tables, size_t max_seqlen_q,
+                                      size_t max_context_len, float softmax_scale, bool causal,
+                                      cudaStream_t stream = cudaStreamPerThread) {
+  const char *fn = "flash_attn_varlen_paged";
+  using detail::require;
+  const int dev = detail::require_cuda(fn, {&q, &key_cache, &value_cache, &seqlens_q, &context_lens, &block_tables});
+  const detail::CacheDims c = detail::cache_dims(fn, key_cache, value_cache);
+  require(fn, q.dim() == 3 && q.size(2) == c.head_size && q.stride(2) == 1,
+          "q must be [total_q, num_heads, head_size] with contiguous last dimension");
+  require(fn, seqlens_q.kind == Kind::Int && context_lens.kind == Kind::Int && block_tables.kind == Kind::Int &&
+                  seqlens_q.is_contiguous() && context_lens.is_contiguous() && block_tables.is_contiguous(),
+          "seqlens_q, context_lens and block_tables must be contiguous int32");
+  const int batch = (int)seqlens_q.numel() - 1;
+  require(fn, batch > 0 && context_lens.numel() == batch && block_tables.dim() == 2 && block_tables.size(0) == batch,
+          "context_lens must be [batch] and block_tables [batch, max_blocks]");
+  Tensor out = Tensor::empty(q.sizes, q.kind, dev);
+  detail::DeviceGuard guard(dev);
+  check(fn, aici_mha_varlen_paged_fwd(out.data, q.data, key_cache.data, value_cache.data,
+                                      static_cast<const int32_t *>(seqlens_q.data),
+                                      static_cast<const int32_t *>(context_lens.data),
+                                      static_cast<const int32_t *>(block_tables.data), batch, (int)q.size(0),
+                                      (int)q.size(1), c.num_kv_heads, c.head_size, c.block_size,
+                                      (int)max_seqlen_q, (int)max_context_len, (int)block_tables.size(1),
+                                      c.num_blocks, q.stride(0), q.stride(1), out.stride(0), out.stride(1),
+                                      key_cache.stride(0), key_cache.stride(1), softmax_scale, causal ? 1 : 0,
+                                      detail::dtype_of(fn, q), stream));
+  return out;
+}
+
+// rotary_embedding (lib.rs:139-146) and reshape_and_cache in one pass, as rLLM issues them back to
+// back (rllm-cuda/src/llm/mod.rs:107-114, 158-164): query and key are rotated in place (NeoX,
+// rot_dim = head_size), the rotated key and value go to the cache at slot_mapping.
+inline void rotary_embedding_reshape_and_cache(const Tensor &positions, Tensor &query, Tensor &key,
+                                               const Tensor &value, const Tensor &cos_sin_cache,
+                                               Tensor &key_cache, Tensor &value_cache,
+                                               const Tensor &slot_mapping, bool is_neox = true,
+                                               cudaStream_t stream = cudaStreamPerThread) {
+  const char *fn = "rotary_embedding_reshape_and_cache";
+  using detail::require;
+  const int dev = detail::require_cuda(fn, {&positions, &query, &key, &value, &cos_sin_cache, &key_cache,
+                                            &value_cache, &slot_mapping});
+  const detail::CacheDims c = detail::check_kv_rows(fn, key, value, key_cache, value_cache, slot_mapping);
+  require(fn, positions.kind == Kind::Int64 && positions.is_contiguous() && positions.numel() == key.size(0),
+          "positions must be contiguous int64 with one entry per token");
+  require(fn, query.dim() == 3 && query.size(0) == key.size(0) && query.size(2) == c.head_size &&
+                  query.stride(2) == 1 && query.stride(1) == c.head_size,
+          "query must be [num_tokens, num_heads, head_size] with contiguous heads");
+  require(fn, cos_sin_cache.dim() == 2 && cos_sin_cache.is_contiguous() && cos_sin_cache.kind == key.kind,
+          "cos_sin_cache must be contiguous [max_position, rot_dim] in the key's dtype");
+  require(fn, slot_mapping.kind == Kind::Int || slot_mapping.kind == Kind::Int64, "slot_mapping must be int32 or int64");
+  detail::DeviceGuard guard(dev);
+  check(fn, aici_rotary_reshape_and_cache(static_cast<const int64_t *>(positions.data), query.data, key.data,
+                                          value.data, cos_sin_cache.data, key_cache.data, value_cache.data,
+                                          slot_mapping.data, slot_mapping.kind == Kind::Int64 ? 1 : 0,
+                                          (int)key.size(0), (int)query.size(1), c.num_kv_heads, c.head_size,
+                                          (int)cos_sin_cache.size(1), is_neox ? 1 : 0, cos_sin_cache.size(0),
+                                          c.block_size, c.num_blocks, query.stride(0), key.stride(0),
+                                          value.stride(0), detail::dtype_of(fn, key), stream));
+}
+
 // Reads and clears the device's sticky status word (no counterpart in the crate; the reference
 // kernels trap or read out of bounds where these record a bit and carry on).
 inline int last_status() {

@@ -34,6 +34,10 @@ void oracle_varlen_attn(float *out_f32, const uint16_t *q, const uint16_t *k, co
                         int num_heads_k, int head_size, int64_t q_tok_stride, int64_t q_head_stride,
                         int64_t k_tok_stride, int64_t k_head_stride, int64_t v_tok_stride,
                         int64_t v_head_stride, float scale, int causal, int p_bf16);
+void oracle_rotary_embedding_neox(const int64_t *positions, uint16_t *query, uint16_t *key,
+                                  const uint16_t *cos_sin_cache, int num_tokens, int num_heads,
+                                  int num_kv_heads, int head_size, int rot_dim, int64_t query_stride,
+                                  int64_t key_stride);
 }
 
 namespace t = aici::tch;
@@ -389,6 +393,75 @@ static void batch_info_feeds_the_decode_kernel() {
   cudaFreeHost(staging);
 }
 
+static void paged_prefill_reads_the_cache_through_block_tables() {
+  // A chunk of new tokens behind a cached prefix: keys/values only exist in the paged cache.
+  Rng r(71);
+  const int hq = 8, hkv = 2;
+  const std::vector<int> lens_k = {200, 70, 33}, lens_q = {72, 70, 1};
+  Paged p(r, 40, hkv, lens_k);
+  const int B = (int)lens_k.size();
+  std::vector<int32_t> cu_q = {0}, cu_k = {0};
+  for (int i = 0; i < B; ++i) {
+    cu_q.push_back(cu_q.back() + lens_q[i]);
+    cu_k.push_back(cu_k.back() + lens_k[i]);
+  }
+  const int tq = cu_q.back(), tk = cu_k.back();
+  auto q = randn_bf16(r, (size_t)tq * hq * 128);
+  // the packed K/V the oracle wants, read out of the cache layout on the host
+  std::vector<uint16_t> k((size_t)tk * hkv * 128), v((size_t)tk * hkv * 128);
+  for (int s = 0; s < B; ++s)
+    for (int tok = 0; tok < lens_k[s]; ++tok)
+      for (int h = 0; h < hkv; ++h)
+        for (int d = 0; d < 128; ++d) {
+          const size_t blk = (size_t)p.rows[s][tok / 16], off = tok % 16;
+          const size_t dst = ((size_t)(cu_k[s] + tok) * hkv + h) * 128 + d;
+          k[dst] = p.kc[(((blk * hkv + h) * 16 + d / 8) * 16 + off) * 8 + d % 8];
+          v[dst] = p.vc[((blk * hkv + h) * 128 + d) * 16 + off];
+        }
+  const float scale = 1.f / std::sqrt(128.f);
+  std::vector<float> want((size_t)tq * hq * 128);
+  oracle_varlen_attn(want.data(), q.data(), k.data(), v.data(), cu_q.data(), cu_k.data(), B, hq, hkv, 128, hq * 128,
+                     128, hkv * 128, 128, hkv * 128, 128, scale, 1, 0);
+  Tensor out = t::flash_attn_varlen_paged(to_device(q, {tq, hq, 128}, Kind::BFloat16), p.key_cache(), p.value_cache(),
+                                          to_device(cu_q, {B + 1}, Kind::Int), to_device(p.ctx, {B}, Kind::Int),
+                                          to_device(p.tables, {B, p.max_blocks}, Kind::Int), 72, 200, scale, true);
+  expect_close(to_host<uint16_t>(out), want, 2e-2f, 2e-3f);
+  EXPECT(t::last_status() == 0, "status word set");
+}
+
+static void rotary_and_cache_write_in_one_pass() {
+  Rng r(81);
+  const int T = 21, hq = 8, hkv = 2, nblk = 6, max_pos = 64;
+  Paged p(r, nblk, hkv, {});
+  auto q = randn_bf16(r, (size_t)T * hq * 128), k = randn_bf16(r, (size_t)T * hkv * 128);
+  auto v = randn_bf16(r, (size_t)T * hkv * 128);
+  std::vector<uint16_t> cs((size_t)max_pos * 128);  // [cos | sin] per position (llm/mod.rs:41-60)
+  for (int pos = 0; pos < max_pos; ++pos)
+    for (int i = 0; i < 64; ++i) {
+      const float a = pos * std::pow(10000.f, -2.f * i / 128.f);
+      cs[(size_t)pos * 128 + i] = to_bf16(std::cos(a));
+      cs[(size_t)pos * 128 + 64 + i] = to_bf16(std::sin(a));
+    }
+  std::vector<int64_t> positions(T), slots(T);
+  for (int i = 0; i < T; ++i) {
+    positions[i] = r.below(max_pos);
+    slots[i] = 3 + i;  // a run that starts in the middle of a block
+  }
+  Tensor dq = to_device(q, {T, hq, 128}, Kind::BFloat16), dk = to_device(k, {T, hkv, 128}, Kind::BFloat16);
+  Tensor kc = p.key_cache(), vc = p.value_cache();
+  t::rotary_embedding_reshape_and_cache(to_device(positions, {T}, Kind::Int64), dq, dk,
+                                        to_device(v, {T, hkv, 128}, Kind::BFloat16),
+                                        to_device(cs, {max_pos, 128}, Kind::BFloat16), kc, vc,
+                                        to_device(slots, {T}, Kind::Int64));
+  oracle_rotary_embedding_neox(positions.data(), q.data(), k.data(), cs.data(), T, hq, hkv, 128, 128, hq * 128, hkv * 128);
+  oracle_reshape_and_cache(k.data(), v.data(), p.kc.data(), p.vc.data(), slots.data(), T, hkv * 128, hkv * 128, hkv, 128,
+                           16, 8);
+  EXPECT(to_host<uint16_t>(dq) == q, "rotated query differs from the oracle");
+  EXPECT(to_host<uint16_t>(dk) == k, "rotated key differs from the oracle");
+  EXPECT(to_host<uint16_t>(kc) == p.kc, "key cache differs from the oracle");
+  EXPECT(to_host<uint16_t>(vc) == p.vc, "value cache differs from the oracle");
+}
+
 struct Test {
   const char *name;
   std::function<void()> fn;
@@ -406,6 +479,8 @@ int main(int argc, char **argv) {
       {"flash_attn_varlen_non_causal_closed_form_inputs", [] { flash_attn_varlen_case({2, 33}, {2, 33}, 3, 3, false, true); }},
       {"errors_carry_the_function_name", errors_carry_the_function_name},
       {"batch_info_feeds_the_decode_kernel", batch_info_feeds_the_decode_kernel},
+      {"paged_prefill_reads_the_cache_through_block_tables", paged_prefill_reads_the_cache_through_block_tables},
+      {"rotary_and_cache_write_in_one_pass", rotary_and_cache_write_in_one_pass},
   };
   if (argc > 1 && std::string(argv[1]) == "--list") {
     for (const Test &tc : tests) std::printf("%s\n", tc.name);
