@@ -102,13 +102,17 @@ char *aici_rotary_reshape_and_cache(const int64_t *positions, void *query, void 
 
 /* ---- decode attention over the paged cache ----------------------------------------- */
 
-/* Tuning hook for benchmarks: tokens per chunk of the context split used by
- * aici_paged_attention_v1 (a multiple of 16 up to 512); 0 restores the batch-adaptive default.
- * Process-wide; changes what aici_paged_attention_workspace_bytes returns. */
+/* Tuning hook for benchmarks and tests.  By default aici_paged_attention_v1 gives every warp of
+ * its grid one run of consecutive 16-token tiles of the whole batch (even load whatever the
+ * context lengths are).  A non-zero value (a multiple of 16 up to 512) selects the other
+ * traversal instead: every sequence is cut into chunks of that many tokens, dealt out round-robin.
+ * 0 restores the default.  Process-wide; changes what aici_paged_attention_workspace_bytes
+ * returns. */
 char *aici_tune_decode_chunk(int chunk_tokens);
 
-/* Bytes of caller-owned scratch aici_paged_attention_v1 needs for these sizes (the chunk size of
- * the context split, and with it the number of partial results, depends on all four). */
+/* Bytes of caller-owned scratch aici_paged_attention_v1 needs for these sizes: about 520 bytes
+ * per query head of a group and (warp of the grid + sequence x kv head) for the default
+ * traversal; per (sequence, head, chunk) for the chunked one. */
 size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads, int num_kv_heads,
                                             int max_context_len);
 
@@ -117,9 +121,9 @@ size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads, int num
  * [num_seqs, num_heads, head_size] (q_stride = query row stride in elements; out is
  * contiguous); block_tables int32 [num_seqs, max_num_blocks_per_seq]; context_lens int32
  * [num_seqs]; kv_block_stride / kv_head_stride in elements.  alibi_slopes must be NULL
- * (rLLM never passes one, rllm-cuda/src/llm/mod.rs:310).  The context is always split into
- * fixed-size chunks that are merged by a second kernel; `workspace` holds the chunk list
- * and the fp32 partial results and must be at least
+ * (rLLM never passes one, rllm-cuda/src/llm/mod.rs:310).  Rows of the batch that more than one
+ * warp worked on are combined by a second kernel; `workspace` holds the traversal's bookkeeping
+ * and the fp32 partial results, needs no initialisation, and must be at least
  * aici_paged_attention_workspace_bytes() large and 256-byte aligned. */
 char *aici_paged_attention_v1(void *out, const void *query, const void *key_cache,
                               const void *value_cache, int num_kv_heads, float scale,
