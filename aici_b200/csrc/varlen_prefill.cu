@@ -328,6 +328,21 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         fence_proxy_async_smem();
         __syncwarp();
       }
+      if (!kPaged && lk - j * kBN < kBN) {
+        // Packed layout, last tile of the sequence: the rows behind it belong to the next sequence
+        // (or were zero-filled past the end of the tensor).  Their probabilities are 0, but 0 x NaN
+        // is NaN, so the rows are cleared as the reference's predicated loads clear them
+        // (flash_fwd_kernel.h, Clear_OOB_MN).  A token row is 128 B in each of the two panels; the
+        // swizzle only permutes bytes inside a row.
+        const int valid = lk - j * kBN;
+        uint8_t *vt = sKV + (i_v % kKvStages) * kTileBytes;
+        for (int idx = valid * 16 + lane; idx < kBN * 16; idx += 32) {
+          const int r = idx >> 4, c = idx & 15;  // row, 16-byte piece (8 per panel)
+          *reinterpret_cast<uint4 *>(vt + (c >> 3) * kPanelBytes + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
       if (j < nt0) {
         if (!wait(&sh->p_ready[0], (uint32_t)j & 1u)) break;
         issue_pv(0, i_v, j == 0, j == nt0 - 1);

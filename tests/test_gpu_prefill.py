@@ -160,6 +160,29 @@ def test_config4_full_size_sampled_rows(cuda_device):
     assert mx <= MAX_ABS and mean <= MEAN_ABS, (mx, mean)
 
 
+def test_neighbour_rows_behind_a_sequence_end_are_ignored(cuda_device):
+    """The last key/value tile of a packed sequence also holds the first rows of the next
+    sequence; NaN/Inf there must not leak (the reference's loads are predicated)."""
+    g = torch.Generator().manual_seed(93)
+    lens = [100, 60, 200]
+    total = sum(lens)
+    q = torch.randn(total, 8, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(total, 2, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(total, 2, 128, generator=g).to(torch.bfloat16)
+    cu = torch.tensor([0, 100, 160, 360], dtype=torch.int32)
+    scale = 1.0 / 128 ** 0.5
+    want = O.flash_attn_varlen(q, k, v, cu, cu, 200, 200, scale, True)
+    kp, vp = k.clone(), v.clone()
+    kp[100:160] = float("nan")   # poison the middle sequence: its own rows become NaN, its
+    vp[100:160] = float("inf")   # neighbours must not notice
+    out = tch_cuda.flash_attn_varlen(q.to(cuda_device), kp.to(cuda_device), vp.to(cuda_device),
+                                     cu.to(cuda_device), cu.to(cuda_device), 200, 200, scale, True).cpu()
+    keep = torch.cat([torch.arange(0, 100), torch.arange(160, 360)])
+    assert torch.isfinite(out[keep].float()).all()
+    mx, mean = O.error_stats(out[keep], want[keep])
+    assert mx <= MAX_ABS and mean <= MEAN_ABS, (mx, mean)
+
+
 def test_rejects_unsupported(cuda_device):
     q = torch.zeros(4, 2, 64, dtype=torch.bfloat16, device=cuda_device)
     cu = torch.tensor([0, 4], dtype=torch.int32, device=cuda_device)
