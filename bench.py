@@ -435,9 +435,11 @@ def run_ours(args):
         },
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h,
-                "note": "q, new k/v, slot map, block tables, context lens copied from pinned host memory "
-                        "and the output read back every step; the KV cache is resident state"},
-        "gpu_launches": 3 * args.steps,  # reshape_and_cache, paged_decode, paged_merge per step
+                "note": "q, new k/v, slot map, block tables, context lens copied from one pinned staging "
+                        "buffer (one copy) and the output read back every step; the KV cache is resident state"},
+        # this library's kernels inside the timed region, per step: reshape_and_cache, paged_decode,
+        # paged_merge, and the cross-GPU barrier kernel when the fused gather is used
+        "gpu_launches": (4 if fused else 3) * args.steps,
         "clocks": clocks,
         "prefill": {
             "workload": pw.name + "_causal_d128", "tflops": p_tflops, "ms_per_step": p_ms, "steps": p_steps,
