@@ -36,6 +36,8 @@ constexpr int kPrefillThreads = 320;   // 8 softmax warps + producer + MMA issue
 constexpr uint32_t kTmemCols = 512;    // S0/P0 [0,128) S1/P1 [128,256) O0 [256,384) O1 [384,512)
 constexpr float kRescaleThreshold = 8.f;  // log2 units: the running reference moves once a score exceeds it by this
 constexpr float kDangerThreshold = 60.f;  // beyond this a tile is redone against its exact maximum (no overflow risk)
+constexpr float kRescaleSum = 256.f;      // single-pass tiles: a row sum above this moves the reference (some score is 2^8 above it, or many are above it)
+constexpr float kDangerSum = 1e30f;       // single-pass tiles: a row sum at or above this (or NaN) means the tile is redone exactly
 
 struct PrefillParams {
   // output [total_q, heads, 128] (strides below) in `world` buffers -- this GPU's and, for the
@@ -417,7 +419,9 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // more than kRescaleThreshold the reference moves after this tile's P V (pending).
         uint32_t pk[64];
         uint32_t ra[32], rb[32];
-        float xmax = -INFINITY, l0 = 0.f, l1 = 0.f;
+        float l0 = 0.f, l1 = 0.f;
+        uint64_t acc2 = pack_f32x2(0.f, 0.f);
+        const uint64_t sc2 = pack_f32x2(sc, sc), nm2 = pack_f32x2(-m_used, -m_used);
         tmem_ld32(t_s, ra);
 #pragma unroll
         for (int c4 = 0; c4 < 4; ++c4) {
@@ -426,14 +430,14 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
           uint32_t(&nxt)[32] = (c4 & 1) ? ra : rb;
           if (c4 < 3) tmem_ld32(t_s + 32 * (c4 + 1), nxt);
           if (full_tile) {
+            // packed fp32 pairs: one FMA and one add per two scores
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float x0 = fmaf(__uint_as_float(cur[i]), sc, -m_used);
-              const float x1 = fmaf(__uint_as_float(cur[i + 1]), sc, -m_used);
-              xmax = fmaxf(xmax, fmaxf(x0, x1));
+              const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(cur[i]), __uint_as_float(cur[i + 1])), sc2, nm2);
+              float x0, x1;
+              unpack_f32x2(x, x0, x1);
               const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-              l0 += p0;
-              l1 += p1;
+              acc2 = add_f32x2(acc2, pack_f32x2(p0, p1));
               pk[16 * c4 + (i >> 1)] = pack_bf16(p0, p1);
             }
           } else {
@@ -442,7 +446,6 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
             for (int i = 0; i < 32; i += 2) {
               const float x0 = (cb + i < lim_row) ? fmaf(__uint_as_float(cur[i]), sc, -m_used) : -INFINITY;
               const float x1 = (cb + i + 1 < lim_row) ? fmaf(__uint_as_float(cur[i + 1]), sc, -m_used) : -INFINITY;
-              xmax = fmaxf(xmax, fmaxf(x0, x1));
               const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
               l0 += p0;
               l1 += p1;
@@ -450,16 +453,28 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
             }
           }
         }
-        if (__any_sync(0xffffffffu, xmax > kDangerThreshold)) {
+        // The tile's row sum tells whether the reference is still good: every score at or below it
+        // gives a sum of at most 128, one score 2^8 above it a sum above 256, and a sum that left
+        // the fp32 range (or is NaN) means the tile has to be redone against its exact maximum.
+        {
+          float a0, a1;
+          unpack_f32x2(acc2, a0, a1);
+          l0 += a0;
+          l1 += a1;
+        }
+        const float l_tile = l0 + l1;
+        if (__any_sync(0xffffffffu, !(l_tile < kDangerSum))) {
           exact_path = true;  // S is untouched: redo the tile with an exact maximum
         } else {
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4)
             tmem_st16(t_s + 16 * c4, *reinterpret_cast<uint32_t(*)[16]>(&pk[16 * c4]));
-          l_sum += l0 + l1;
-          if (xmax > kRescaleThreshold) {
+          l_sum += l_tile;
+          if (l_tile > kRescaleSum) {
+            // log2 of the sum bounds the largest score from above (by at most 7): a reference a few
+            // powers of two above the maximum costs bf16 and fp32 nothing
             pending = true;
-            m_next = m_used + xmax;
+            m_next = m_used + __log2f(l_tile);
           }
         }
       }

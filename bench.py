@@ -221,10 +221,23 @@ def run_ours(args):
     decode_bytes_local = w.algorithmic_bytes()
     fused = world > 1 and args.gather == "fused"
     pg = None
+    fused_fallback = None
     if fused:
         from aici_b200 import sharding
-        pg = sharding.PeerGather(S, hq_local * world, 128, dev)
-        pg.barrier()
+        # peer-mapped buffers come from torch's symmetric-memory allocator; if any rank cannot set
+        # them up, every rank falls back to the NCCL gather (and the JSON line says so)
+        try:
+            pg = sharding.PeerGather(S, hq_local * world, 128, dev)
+            ok = 1
+        except Exception as e:  # noqa: BLE001
+            fused_fallback, ok = "%s: %s" % (type(e).__name__, str(e)[:120]), 0
+        flag = torch.tensor([ok], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            fused, pg = False, None
+            fused_fallback = fused_fallback or "another rank could not map peer memory"
+        else:
+            pg.barrier()
 
     def attention(q, bt, cl):
         """decode attention + head gather: fused epilogue (peer stores + barrier) or NCCL all-gather"""
@@ -438,7 +451,8 @@ def run_ours(args):
             "collective": ("none" if world == 1 else
                            "fused: attention epilogue stores head outputs into every rank's buffer over "
                            "NVLink (peer-mapped symmetric memory), then a signal barrier" if fused else
-                           "nccl all_gather of head outputs"),
+                           "nccl all_gather of head outputs" +
+                           (" (fused gather unavailable: %s)" % fused_fallback if fused_fallback else "")),
         },
         "roofline": {
             "kernel": "paged_decode_kernel (+ plan and merge launches of the same call)",
