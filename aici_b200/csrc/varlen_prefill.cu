@@ -35,7 +35,6 @@ constexpr int kKvStages = 4;           // ring of K/V tiles (K_j and V_j alterna
 constexpr int kPrefillThreads = 320;   // 8 softmax warps + producer + MMA issuer
 constexpr uint32_t kTmemCols = 512;    // S0/P0 [0,128) S1/P1 [128,256) O0 [256,384) O1 [384,512)
 constexpr float kRescaleThreshold = 8.f;  // log2 units: the running reference moves once a score exceeds it by this
-constexpr float kDangerThreshold = 60.f;  // beyond this a tile is redone against its exact maximum (no overflow risk)
 constexpr float kRescaleSum = 256.f;      // single-pass tiles: a row sum above this moves the reference (some score is 2^8 above it, or many are above it)
 constexpr float kDangerSum = 1e30f;       // single-pass tiles: a row sum at or above this (or NaN) means the tile is redone exactly
 
@@ -415,8 +414,9 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (!exact_path) {
         // ---- single pass against the running reference m_used --------------------------------
         // P is computed for the whole row in registers while S is still intact; if some score
-        // exceeds the reference by more than kDangerThreshold the tile is redone exactly, if by
-        // more than kRescaleThreshold the reference moves after this tile's P V (pending).
+        // left the reference so far behind that the row sum nears the end of the fp32 range the tile
+        // is redone exactly; if the row sum shows a score 2^8 above the reference (see below), the
+        // reference moves after this tile's P V (pending).
         uint32_t pk[64];
         uint32_t ra[32], rb[32];
         float l0 = 0.f, l1 = 0.f;
@@ -444,11 +444,12 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const int cb = n0 + 32 * c4;
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float x0 = (cb + i < lim_row) ? fmaf(__uint_as_float(cur[i]), sc, -m_used) : -INFINITY;
-              const float x1 = (cb + i + 1 < lim_row) ? fmaf(__uint_as_float(cur[i + 1]), sc, -m_used) : -INFINITY;
-              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-              l0 += p0;
-              l1 += p1;
+              const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(cur[i]), __uint_as_float(cur[i + 1])), sc2, nm2);
+              float x0, x1;
+              unpack_f32x2(x, x0, x1);
+              const float p0 = fast_exp2((cb + i < lim_row) ? x0 : -INFINITY);
+              const float p1 = fast_exp2((cb + i + 1 < lim_row) ? x1 : -INFINITY);
+              acc2 = add_f32x2(acc2, pack_f32x2(p0, p1));
               pk[16 * c4 + (i >> 1)] = pack_bf16(p0, p1);
             }
           }
@@ -531,13 +532,19 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
           const int cb = n0 + 32 * c4;
           uint32_t pk[16];
           if (cb + 32 <= lim_row) {
+            const uint64_t sc2 = pack_f32x2(sc, sc), nb2 = pack_f32x2(-base, -base);
+            uint64_t acc2 = pack_f32x2(0.f, 0.f);
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), sc, -base));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), sc, -base));
-              l_sum += p0 + p1;
+              float x0, x1;
+              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sc2, nb2), x0, x1);
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              acc2 = add_f32x2(acc2, pack_f32x2(p0, p1));
               pk[i >> 1] = pack_bf16(p0, p1);
             }
+            float a0, a1;
+            unpack_f32x2(acc2, a0, a1);
+            l_sum += a0 + a1;
           } else {
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
