@@ -290,12 +290,11 @@ def run_ours(args):
             step()
         ev1.record()
         barrier()
-    # the decode call alone (decode + merge launches), timed per step with events, eagerly
-    att_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-              for _ in range(args.steps)]
-    for i in range(args.steps):
-        tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
-        att_ev[i][0].record()
+    # The decode call alone (decode + merge launches; with the fused gather their stores to the
+    # peers), for the roofline: K back-to-back replays of a graph holding just that call, so the
+    # figure is device time and does not depend on how fast the host can launch (eager launches
+    # with per-step events when graphs are off).
+    def attention_only():
         if fused:
             tch_cuda.paged_attention_v1_peers(pg.ptrs, hq_local * world, pg.head0, w.query, w.key_cache,
                                               w.value_cache, w.num_kv_heads, w.scale, w.block_tables,
@@ -303,15 +302,40 @@ def run_ours(args):
         else:
             tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
                                         w.block_tables, w.context_lens, 16, w.max_context_len, None)
-        att_ev[i][1].record()
-        if fused:
-            pg.barrier()
-        elif world > 1:
-            dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), out)
+
+    if use_graph:
+        side.wait_stream(torch.cuda.current_stream(dev))
+        att_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(att_graph, stream=side):
+            attention_only()
+        for _ in range(3):
+            att_graph.replay()
+        barrier()
+        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ea.record()
+        for _ in range(args.steps):
+            att_graph.replay()
+        eb.record()
+        barrier()
+        att_local_ms = ea.elapsed_time(eb) / args.steps
+    else:
+        att_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                  for _ in range(args.steps)]
+        for i in range(args.steps):
+            tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
+            att_ev[i][0].record()
+            attention_only()
+            att_ev[i][1].record()
+            if fused:
+                pg.barrier()
+            elif world > 1:
+                dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), out)
+        barrier()
+        att_local_ms = sum(a.elapsed_time(b) for a, b in att_ev) / args.steps
     barrier()
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     ms_step = ms_total / args.steps
-    att_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in att_ev) / args.steps)
+    att_ms = max_over_ranks(att_local_ms)
     status = _lib.last_status()
     if status != 0:
         raise SystemExit("device status word is %d after the timed region" % status)
