@@ -410,7 +410,9 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
 
       const bool full_tile = n0 + kBN <= lim_row;
-      bool exact_path = (j == 0) || __any_sync(0xffffffffu, m_used == -INFINITY);
+      // rows that have not seen a single column so far have no reference yet: exact path, except on
+      // the first tile, which takes its reference from its own first 32 columns (below)
+      bool exact_path = (j > 0) && __any_sync(0xffffffffu, m_used == -INFINITY);
       if (!exact_path) {
         // ---- single pass against the running reference m_used --------------------------------
         // P is computed for the whole row in registers while S is still intact; if some score
@@ -421,8 +423,20 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         uint32_t ra[32], rb[32];
         float l0 = 0.f, l1 = 0.f;
         uint64_t acc2 = pack_f32x2(0.f, 0.f);
-        const uint64_t sc2 = pack_f32x2(sc, sc), nm2 = pack_f32x2(-m_used, -m_used);
         tmem_ld32(t_s, ra);
+        if (j == 0) {
+          // First tile: the reference is the largest visible score among the first 32 columns (the
+          // visible columns of a row are a prefix, so a row that sees nothing here sees nothing in
+          // the tile).  If the rest of the tile lies far above it, the row sum says so as usual.
+          tmem_wait_ld();
+          float mx = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < lim_row) mx = fmaxf(mx, __uint_as_float(ra[i]));
+          m_used = mx * sc;  // scale > 0 keeps the order
+        }
+        const float ref = (m_used == -INFINITY) ? 0.f : m_used;
+        const uint64_t sc2 = pack_f32x2(sc, sc), nm2 = pack_f32x2(-ref, -ref);
 #pragma unroll
         for (int c4 = 0; c4 < 4; ++c4) {
           tmem_wait_ld();
