@@ -163,6 +163,21 @@ __device__ __forceinline__ void tma_load_5d(void *dst_smem, const CUtensorMap *t
       : "memory");
 }
 
+// Tiled TMA store shared -> global (bulk async-group completion).  Same alignment rule as the
+// loads for the innermost coordinate; never started at a negative coordinate.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *tmap, const void *src_smem, int c0, int c1,
+                                             int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tmap),
+               "r"(smem_u32(src_smem)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+// Closes the group of stores issued so far by this thread and waits until the engine has read
+// their shared-memory source (the global writes may still be in flight).
+__device__ __forceinline__ void tma_store_commit_and_wait_read() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

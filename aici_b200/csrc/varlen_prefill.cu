@@ -49,6 +49,8 @@ struct PrefillParams {
   int group;
   int causal;
   int pair_heads;  // 1: the two tiles are heads 2y and 2y+1; 0: two consecutive row tiles of head y
+  int tma_store;   // 1: full output tiles leave shared memory as TMA stores (one output buffer only)
+  int total_q;     // rows of the packed query / output tensors
   float scale_log2e;
   unsigned int *status;
   // paged variant: keys/values are read from the KV cache through the block table
@@ -94,7 +96,8 @@ template <bool kPaged>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
-                      const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
+                      const __grid_constant__ CUtensorMap tmap_v,
+                      const __grid_constant__ CUtensorMap tmap_o, const PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.z;
@@ -586,7 +589,9 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if (ok) {
       tc_fence_after();
       const float inv = l_sum > 0.f ? __fdividef(1.f, l_sum) : 0.f;
-      // staging tile [128 rows][128 bf16] over the Q buffer, 16-byte chunks XOR-swizzled by row
+      // staging tile over the Q buffer in the layout Q arrived in: two panels of [128 rows][64 bf16]
+      // with the 128-byte swizzle (16-byte chunk c of a row sits at chunk c ^ (row & 7)), so that a
+      // TMA store can take it as it is
       uint8_t *stage = sQt;
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) {
@@ -601,23 +606,34 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
           v.z = pack_bf16(__uint_as_float(r[8 * q + 4]) * inv, __uint_as_float(r[8 * q + 5]) * inv);
           v.w = pack_bf16(__uint_as_float(r[8 * q + 6]) * inv, __uint_as_float(r[8 * q + 7]) * inv);
           const int chunk = 4 * c4 + q;
-          *reinterpret_cast<uint4 *>(stage + row * 256 + ((chunk ^ (row & 7)) << 4)) = v;
+          *reinterpret_cast<uint4 *>(stage + (chunk >> 3) * kPanelBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4)) = v;
         }
       }
       // the four warps meet on an mbarrier (bounded wait) rather than a hardware barrier, so a
       // warp that unwound early cannot leave the others waiting forever
+      fence_proxy_async_smem();  // a TMA store may read what this thread just wrote
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->staged[t]);
       ok = __all_sync(0xffffffffu, mbar_wait(&sh->staged[t], 0, p.status));
     }
-    if (ok) {
+    // A tile whose 128 rows all belong to this sequence, or whose sequence ends exactly where the
+    // tensor ends (the copy is clipped there), goes out as two TMA stores; any other tile must not
+    // touch rows that are not its own and is written row by row.
+    const bool whole = p.tma_store && (T.rows == kBM || q0 + lq == p.total_q);
+    if (ok && whole) {
+      if (wtid == 0) {
+        tma_store_3d(&tmap_o, sQt, 0, T.h, q0 + T.m0);
+        tma_store_3d(&tmap_o, sQt + kPanelBytes, 64, T.h, q0 + T.m0);
+        tma_store_commit_and_wait_read();  // shared memory must outlive the engine's reads
+      }
+    } else if (ok) {
       const uint8_t *stage = sQt;
       const int64_t obase = (int64_t)(q0 + T.m0) * p.o_tok_stride + (int64_t)(p.out_head0 + T.h) * p.o_head_stride;
 #pragma unroll 4
       for (int it = 0; it < 16; ++it) {
         const int rr = it * 8 + (wtid >> 4), chunk = wtid & 15;
         if (rr < T.rows) {
-          const uint4 v = *reinterpret_cast<const uint4 *>(stage + rr * 256 + ((chunk ^ (rr & 7)) << 4));
+          const uint4 v = *reinterpret_cast<const uint4 *>(stage + (chunk >> 3) * kPanelBytes + rr * 128 + (((chunk & 7) ^ (rr & 7)) << 4));
           const int64_t off = obase + (int64_t)rr * p.o_tok_stride + chunk * 8;
           for (int w = 0; w < p.world; ++w) *reinterpret_cast<uint4 *>(p.out[w] + off) = v;
         }
@@ -683,8 +699,8 @@ static char *make_tmap(const char *fn, CUtensorMap *map, const void *base, int64
 
 template <bool kPaged>
 static char *launch_prefill(const char *fn, const CUtensorMap &tq, const CUtensorMap &tk,
-                            const CUtensorMap &tv, PrefillParams &p, int num_heads, int batch,
-                            int max_seqlen_q, cudaStream_t stream) {
+                            const CUtensorMap &tv, const CUtensorMap &to, PrefillParams &p, int num_heads,
+                            int batch, int max_seqlen_q, cudaStream_t stream) {
   static bool attr_set[64] = {false};
   int dev = 0;
   AICI_CUDA(cudaGetDevice(&dev));
@@ -697,7 +713,7 @@ static char *launch_prefill(const char *fn, const CUtensorMap &tq, const CUtenso
   p.pair_heads = (p.group % 2 == 0) ? 1 : 0;
   const int mblocks = (max_seqlen_q + kBM - 1) / kBM;
   dim3 grid(p.pair_heads ? mblocks : (mblocks + 1) / 2, p.pair_heads ? num_heads / 2 : num_heads, batch);
-  varlen_prefill_kernel<kPaged><<<grid, kPrefillThreads, kPrefillSmemBytes, stream>>>(tq, tk, tv, p);
+  varlen_prefill_kernel<kPaged><<<grid, kPrefillThreads, kPrefillSmemBytes, stream>>>(tq, tk, tv, to, p);
   AICI_CUDA(cudaGetLastError());
   (void)fn;
   return nullptr;
@@ -768,7 +784,14 @@ static char *mha_varlen_fwd_impl(const char *fn, void *const *outs, int world, i
   p.k_lens = nullptr;
   p.max_blocks = 0;
   p.num_blocks = 0;
-  return launch_prefill<false>(fn, tq, tk, tv, p, num_heads, batch, max_seqlen_q,
+  // the output goes out through a tensor map like the query's when there is one output buffer
+  // (peer buffers of the fused gather are written row by row)
+  CUtensorMap to = tq;
+  p.total_q = total_q;
+  p.tma_store = (world == 1 && out_head0 == 0) ? 1 : 0;
+  if (p.tma_store)
+    if (char *e = make_tmap(fn, &to, out, total_q, num_heads, o_tok_stride, o_head_stride)) return e;
+  return launch_prefill<false>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q,
                                static_cast<cudaStream_t>(stream));
 }
 
@@ -883,6 +906,10 @@ extern "C" char *aici_mha_varlen_paged_fwd(void *out, const void *q, const void 
   p.max_blocks = max_num_blocks_per_seq;
   p.num_blocks = num_blocks;
   (void)max_context_len;
-  return launch_prefill<true>(fn, tq, tk, tv, p, num_heads, batch, max_seqlen_q,
+  CUtensorMap to;
+  p.total_q = total_q;
+  p.tma_store = 1;
+  if (char *e = make_tmap(fn, &to, out, total_q, num_heads, o_tok_stride, o_head_stride)) return e;
+  return launch_prefill<true>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q,
                               static_cast<cudaStream_t>(stream));
 }
