@@ -60,6 +60,11 @@ struct PrefillParams {
   int64_t num_blocks;
 };
 
+// One tensor map per output buffer (this GPU's and, for the fused gather, every peer's).
+struct OutMaps {
+  CUtensorMap m[8];
+};
+
 struct PrefillSmem {
   uint64_t q_full[2], kv_full[kKvStages], kv_empty[kKvStages], s_full[2], p_ready[2], o_full[2], staged[2], drain;
   uint32_t tmem_base;
@@ -97,7 +102,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1)
 varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v,
-                      const __grid_constant__ CUtensorMap tmap_o, const PrefillParams p) {
+                      const __grid_constant__ OutMaps tmap_o, const PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.z;
@@ -622,9 +627,13 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const bool whole = p.tma_store && (T.rows == kBM || q0 + lq == p.total_q);
     if (ok && whole) {
       if (wtid == 0) {
-        tma_store_3d(&tmap_o, sQt, 0, T.h, q0 + T.m0);
-        tma_store_3d(&tmap_o, sQt + kPanelBytes, 64, T.h, q0 + T.m0);
-        tma_store_commit_and_wait_read();  // shared memory must outlive the engine's reads
+        for (int w = 0; w < p.world; ++w) {  // peers' buffers are plain global addresses to the engine
+          tma_store_3d(&tmap_o.m[w], sQt, 0, p.out_head0 + T.h, q0 + T.m0);
+          tma_store_3d(&tmap_o.m[w], sQt + kPanelBytes, 64, p.out_head0 + T.h, q0 + T.m0);
+        }
+        // shared memory must outlive the engine's reads; with peers the writes themselves are
+        // awaited too, so that they are done when this grid is and the barrier kernel may signal
+        if (p.world > 1) tma_store_commit_and_wait_all(); else tma_store_commit_and_wait_read();
       }
     } else if (ok) {
       const uint8_t *stage = sQt;
@@ -699,7 +708,7 @@ static char *make_tmap(const char *fn, CUtensorMap *map, const void *base, int64
 
 template <bool kPaged>
 static char *launch_prefill(const char *fn, const CUtensorMap &tq, const CUtensorMap &tk,
-                            const CUtensorMap &tv, const CUtensorMap &to, PrefillParams &p, int num_heads,
+                            const CUtensorMap &tv, const OutMaps &to, PrefillParams &p, int num_heads,
                             int batch, int max_seqlen_q, cudaStream_t stream) {
   static bool attr_set[64] = {false};
   int dev = 0;
@@ -784,13 +793,14 @@ static char *mha_varlen_fwd_impl(const char *fn, void *const *outs, int world, i
   p.k_lens = nullptr;
   p.max_blocks = 0;
   p.num_blocks = 0;
-  // the output goes out through a tensor map like the query's when there is one output buffer
-  // (peer buffers of the fused gather are written row by row)
-  CUtensorMap to = tq;
+  // every output buffer gets a tensor map like the query's; this rank's heads start at out_head0
+  OutMaps to;
   p.total_q = total_q;
-  p.tma_store = (world == 1 && out_head0 == 0) ? 1 : 0;
-  if (p.tma_store)
-    if (char *e = make_tmap(fn, &to, out, total_q, num_heads, o_tok_stride, o_head_stride)) return e;
+  p.tma_store = 1;
+  for (int w = 0; w < 8; ++w)
+    if (char *e = make_tmap(fn, &to.m[w], outs[w < world ? w : 0], total_q, out_head0 + num_heads, o_tok_stride,
+                            o_head_stride))
+      return e;
   return launch_prefill<false>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q,
                                static_cast<cudaStream_t>(stream));
 }
@@ -906,10 +916,11 @@ extern "C" char *aici_mha_varlen_paged_fwd(void *out, const void *q, const void 
   p.max_blocks = max_num_blocks_per_seq;
   p.num_blocks = num_blocks;
   (void)max_context_len;
-  CUtensorMap to;
+  OutMaps to;
   p.total_q = total_q;
   p.tma_store = 1;
-  if (char *e = make_tmap(fn, &to, out, total_q, num_heads, o_tok_stride, o_head_stride)) return e;
+  for (int w = 0; w < 8; ++w)
+    if (char *e = make_tmap(fn, &to.m[w], out, total_q, num_heads, o_tok_stride, o_head_stride)) return e;
   return launch_prefill<true>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q,
                               static_cast<cudaStream_t>(stream));
 }
