@@ -18,9 +18,10 @@
 //               the tensor pipe works on one tile while the other tile's softmax runs.
 //   warps 0-3 : softmax of tile 0, warps 4-7: softmax of tile 1.  One query row per thread (= one
 //               TMEM lane): tcgen05.ld the scores, mask, exp2 against a running reference maximum
-//               (single pass; the reference moves lazily and a tile whose scores jump too far is
-//               redone exactly), row sum, bf16 P written back with tcgen05.st; at the end
-//               O / sum -> bf16 -> swizzled staging in the tile's Q buffer -> coalesced stores.
+//               (single pass on packed fp32 pairs; the reference moves lazily, judged by the tile's
+//               row sum, and a tile whose scores jump too far is redone exactly), bf16 P written
+//               back with tcgen05.st; at the end O / sum -> bf16 -> staging in the tile's Q buffer
+//               (same swizzled layout) -> TMA stores, or row-by-row stores for a ragged tile.
 // Every barrier wait is bounded; a timeout sets AICI_STATUS_WAIT_TIMEOUT and unwinds.
 #include "tcgen05.cuh"
 
