@@ -22,9 +22,11 @@ static int64_t place(int64_t *cursor, int64_t bytes) {
 }
 
 // Validates the entries, decides their order and fills every field of `lay`.
+// check_slots: also walk the block-start slots (one cache line each); the builder does that walk
+// itself while it fills the tables, so it asks for sizes only.
 static char *plan_batch(const char *fn, const aici_batch_entry *entries, int n, int flags,
                         int block_size, int64_t max_model_len, aici_batch_layout *lay,
-                        std::vector<int> *order) {
+                        std::vector<int> *order, bool check_slots) {
   AICI_CHECK(lay != nullptr, "%s: layout is NULL", fn);
   AICI_CHECK(n > 0 && entries != nullptr, "%s: a step needs at least one sequence", fn);
   AICI_CHECK(block_size > 0, "%s: block_size must be positive", fn);
@@ -70,7 +72,7 @@ static char *plan_batch(const char *fn, const aici_batch_entry *entries, int n, 
     if (!multi || all_tables) {
       const int nb = (e.k_len + block_size - 1) / block_size;
       max_blocks = nb > max_blocks ? nb : max_blocks;
-      for (int t = 0; t < e.k_len; t += block_size) {
+      for (int t = 0; check_slots && t < e.k_len; t += block_size) {
         const int64_t slot = e.kv_slots[t];
         AICI_CHECK(slot >= 0 && slot % block_size == 0 && slot / block_size <= INT32_MAX,
                    "%s: sequence %lld: slot %lld at token %d does not start a block of %d", fn,
@@ -116,7 +118,7 @@ extern "C" char *aici_batch_info_layout(const aici_batch_entry *entries, int num
                                         aici_batch_layout *layout) {
   std::vector<int> order;
   return plan_batch("aici_batch_info_layout", entries, num_entries, flags, block_size,
-                    max_model_len, layout, &order);
+                    max_model_len, layout, &order, true);
 }
 
 extern "C" char *aici_batch_info_build(const aici_batch_entry *entries, int num_entries, int flags,
@@ -126,7 +128,8 @@ extern "C" char *aici_batch_info_build(const aici_batch_entry *entries, int num_
                                        aici_stream_t stream) {
   const char *fn = "aici_batch_info_build";
   std::vector<int> order;
-  if (char *e = plan_batch(fn, entries, num_entries, flags, block_size, max_model_len, layout, &order))
+  if (char *e = plan_batch(fn, entries, num_entries, flags, block_size, max_model_len, layout, &order,
+                           false))
     return e;
   const aici_batch_layout &lay = *layout;
   AICI_CHECK(staging != nullptr && staging_bytes >= (size_t)lay.total_bytes,
@@ -179,8 +182,13 @@ extern "C" char *aici_batch_info_build(const aici_batch_entry *entries, int num_
       const int row = multi ? idx : lay.paged_row0 + (idx - lay.num_multitoken);
       context_lens[row] = e.k_len;
       int32_t *table = block_tables + (size_t)row * lay.max_blocks_per_seq;
-      for (int t = 0, b = 0; t < e.k_len; t += block_size, ++b)
-        table[b] = static_cast<int32_t>(e.kv_slots[t] / block_size);
+      for (int t = 0, b = 0; t < e.k_len; t += block_size, ++b) {
+        const int64_t slot = e.kv_slots[t];
+        AICI_CHECK(slot >= 0 && slot % block_size == 0 && slot / block_size <= INT32_MAX,
+                   "%s: sequence %lld: slot %lld at token %d does not start a block of %d", fn,
+                   (long long)e.seq_id, (long long)slot, t, block_size);
+        table[b] = static_cast<int32_t>(slot / block_size);
+      }
     }
   }
   seqlens_q[lay.num_multitoken] = off_q;
