@@ -19,8 +19,9 @@ EXPORTS = (
     "aici_rotary_reshape_and_cache",
     "aici_copy_blocks",
     "aici_copy_blocks_host",
-    "aici_tune_decode_chunk",
     "aici_paged_attention_workspace_bytes",
+    "aici_paged_attention_chunked_workspace_bytes",
+    "aici_paged_attention_v1_chunked",
     "aici_paged_attention_v1",
     "aici_paged_attention_v2",
     "aici_paged_attention_v1_static",
@@ -29,6 +30,12 @@ EXPORTS = (
     "aici_paged_attention_v1_peers",
     "aici_mha_varlen_fwd_peers",
     "aici_peer_barrier",
+    "aici_paged_attention_v1_peers_barrier",
+    "aici_peer_alloc",
+    "aici_peer_open",
+    "aici_peer_close",
+    "aici_peer_free",
+    "aici_gather_heads",
     "aici_swap_blocks",
     "aici_batch_info_layout",
     "aici_batch_info_build",
@@ -52,9 +59,11 @@ def lib() -> ctypes.CDLL:
         _lib = ctypes.CDLL(LIB_PATH)
         _lib.aici_version.restype = ctypes.c_char_p
         _lib.aici_paged_attention_workspace_bytes.restype = ctypes.c_size_t
+        _lib.aici_paged_attention_chunked_workspace_bytes.restype = ctypes.c_size_t
         for name in EXPORTS:
             fn = getattr(_lib, name)
-            if name not in ("aici_version", "aici_paged_attention_workspace_bytes"):
+            if name not in ("aici_version", "aici_paged_attention_workspace_bytes",
+                            "aici_paged_attention_chunked_workspace_bytes"):
                 fn.restype = ctypes.c_void_p  # char*, released with free()
         _libc = ctypes.CDLL(None)
         _libc.free.argtypes = [ctypes.c_void_p]

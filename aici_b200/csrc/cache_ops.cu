@@ -22,54 +22,61 @@ __device__ __forceinline__ int64_t load_slot(const void *slots, int64_t i) {
   return static_cast<int64_t>(static_cast<const int32_t *>(slots)[i]);
 }
 
-// Writes the CTA's staged value tile s_v[tok][d] (16 tokens x 128) to the cache.
+// Writes the CTA's staged value tile s_v[tok][d] (kT tokens x 128) to the cache.
+template <int kT>
 __device__ __forceinline__ void store_value_tile(const int64_t *s_slot,
                                                  const __nv_bfloat16 (*s_v)[kD + 8],
                                                  __nv_bfloat16 *__restrict__ value_cache,
                                                  int num_kv_heads, int h, int tid) {
-  // aligned: both 8-token halves are runs of consecutive slots starting at a multiple of 8 (the
+  // aligned: every 8-token group is a run of consecutive slots starting at a multiple of 8 (the
   // prefill case: a sequence's tokens fill whole cache blocks in order)
   bool aligned = true;
 #pragma unroll
-  for (int tb = 0; tb < kTok; tb += 8) {
+  for (int tb = 0; tb < kT; tb += 8) {
     const int64_t s0 = s_slot[tb];
     aligned = aligned && s0 >= 0 && (s0 % 8) == 0;
 #pragma unroll
     for (int j = 1; j < 8; ++j) aligned = aligned && (s_slot[tb + j] == s0 + j);
   }
   if (aligned) {
-    // a warp covers 32 consecutive d of one token half: column reads hit 16 distinct banks
-    const int d = tid & (kD - 1), half = tid >> 7;
-    const int tb = half * 8;
-    const int64_t s0 = s_slot[tb];
-    uint4 val;
-    __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&val);
+    // a warp covers 32 consecutive d of one token group: column reads hit 16 distinct banks
 #pragma unroll
-    for (int j = 0; j < 8; ++j) e[j] = s_v[tb + j][d];
-    const int64_t blk = s0 / kB, off = s0 % kB;
-    *reinterpret_cast<uint4 *>(value_cache + ((blk * num_kv_heads + h) * kD + d) * kB + off) = val;
+    for (int u = 0; u < kT / 16; ++u) {
+      const int item = u * kThreads + tid;
+      const int d = item & (kD - 1), tb = (item >> 7) * 8;
+      const int64_t s0 = s_slot[tb];
+      uint4 val;
+      __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&val);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = s_v[tb + j][d];
+      const int64_t blk = s0 / kB, off = s0 % kB;
+      *reinterpret_cast<uint4 *>(value_cache + ((blk * num_kv_heads + h) * kD + d) * kB + off) = val;
+    }
   } else {
     // any slots (decode steps, chunks that start in the middle of a block, skipped tokens):
-    // 16 consecutive threads take the 16 tokens of one d, so tokens with consecutive slots
-    // still land in one 32-byte sector per store instruction
-    const int tok = tid & (kTok - 1);
+    // consecutive threads take the tokens of one d, so tokens with consecutive slots still land
+    // in one 32-byte sector per store instruction
+    const int tok = tid & (kT - 1);
     const int64_t slot = s_slot[tok];
     if (slot >= 0) {
       const int64_t blk = slot / kB, off = slot % kB;
       __nv_bfloat16 *dst = value_cache + (blk * num_kv_heads + h) * (int64_t)(kD * kB) + off;
-#pragma unroll
-      for (int d = tid >> 4; d < kD; d += kThreads / kTok) dst[(int64_t)d * kB] = s_v[tok][d];
+#pragma unroll 4
+      for (int d = tid / kT; d < kD; d += kThreads / kT) dst[(int64_t)d * kB] = s_v[tok][d];
     }
   }
 }
 
-// One CTA moves kTok consecutive tokens of one kv head.
+// One CTA moves kT (16 or 32) consecutive tokens of one kv head.
 //   K: chunk c (8 elements) of token t -> key_cache[blk][h][c][off][0..7]   (16 B vector)
 //   V: element d of token t            -> value_cache[blk][h][d][off]       (2 B, 32 B apart)
-// For V the CTA transposes its [kTok][128] tile in shared memory; a thread then owns one
-// (d, half) pair and writes 8 tokens as one 16-byte store when their slots are consecutive
-// and 8-aligned inside one block (the prefill case), else element by element (decode).
-template <bool kSlot64>
+// Every global load of the CTA -- the slots, the key vectors, the value vectors -- is issued before
+// anything waits: where a token goes does not change what is read, so the three reads share one
+// memory round trip and only the stores depend on the slots.  For V the CTA transposes its
+// [kT][128] tile in shared memory; a thread then owns (d, 8-token group) pairs and writes 8 tokens
+// as one 16-byte store when their slots are consecutive and 8-aligned inside one block (the prefill
+// case), else element by element (decode).
+template <bool kSlot64, int kT>
 __global__ void __launch_bounds__(kThreads)
 reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
                          const __nv_bfloat16 *__restrict__ value,
@@ -78,13 +85,29 @@ reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
                          const void *__restrict__ slot_mapping, int num_tokens, int num_kv_heads,
                          int64_t num_slots, int64_t key_stride, int64_t value_stride,
                          unsigned int *status) {
-  __shared__ int64_t s_slot[kTok];
-  __shared__ __align__(16) __nv_bfloat16 s_v[kTok][kD + 8];  // [tok][d], rows of 272 B
-  const int t0 = blockIdx.x * kTok;
+  __shared__ int64_t s_slot[kT];
+  __shared__ __align__(16) __nv_bfloat16 s_v[kT][kD + 8];  // [tok][d], rows of 272 B
+  constexpr int kPer = kT / 16;  // 16-token groups per CTA = key and value vectors per thread
+  const int t0 = blockIdx.x * kT;
   const int h = blockIdx.y;
   const int tid = threadIdx.x;
 
-  if (tid < kTok) {
+  // K: thread (c, tok) of group u; 16 consecutive threads cover 16 tokens of one chunk, a warp two
+  // neighbouring chunks (whole 32-byte sectors).  V: thread (tok, part); 16 threads read one row.
+  uint4 kvec[kPer], vvec[kPer];
+  const int kc = tid >> 4, ktok = tid & 15;
+  const int vtok = tid >> 4, vpart = tid & 15;
+#pragma unroll
+  for (int u = 0; u < kPer; ++u) {
+    kvec[u] = make_uint4(0, 0, 0, 0);
+    vvec[u] = make_uint4(0, 0, 0, 0);
+    if (t0 + 16 * u + ktok < num_tokens)
+      kvec[u] = *reinterpret_cast<const uint4 *>(key + (int64_t)(t0 + 16 * u + ktok) * key_stride + h * kD + kc * kX);
+    if (t0 + 16 * u + vtok < num_tokens)
+      vvec[u] = *reinterpret_cast<const uint4 *>(value + (int64_t)(t0 + 16 * u + vtok) * value_stride + h * kD +
+                                                 vpart * kX);
+  }
+  if (tid < kT) {
     int64_t slot = -1;
     if (t0 + tid < num_tokens) {
       slot = load_slot<kSlot64>(slot_mapping, t0 + tid);
@@ -95,30 +118,20 @@ reshape_and_cache_kernel(const __nv_bfloat16 *__restrict__ key,
     }
     s_slot[tid] = slot;
   }
+#pragma unroll
+  for (int u = 0; u < kPer; ++u) *reinterpret_cast<uint4 *>(&s_v[16 * u + vtok][vpart * kX]) = vvec[u];
   __syncthreads();
 
-  // ---- K: thread (c, tok); 16 consecutive threads cover 16 tokens of one chunk ----------
-  {
-    const int c = tid >> 4, tok = tid & 15;
-    const int64_t slot = s_slot[tok];
+#pragma unroll
+  for (int u = 0; u < kPer; ++u) {
+    const int64_t slot = s_slot[16 * u + ktok];
     if (slot >= 0) {
       const int64_t blk = slot / kB, off = slot % kB;
-      const uint4 val = *reinterpret_cast<const uint4 *>(key + (int64_t)(t0 + tok) * key_stride +
-                                                         h * kD + c * kX);
-      __nv_bfloat16 *dst =
-          key_cache + ((blk * num_kv_heads + h) * (kD / kX) + c) * (kB * kX) + off * kX;
-      *reinterpret_cast<uint4 *>(dst) = val;
+      __nv_bfloat16 *dst = key_cache + ((blk * num_kv_heads + h) * (kD / kX) + kc) * (kB * kX) + off * kX;
+      *reinterpret_cast<uint4 *>(dst) = kvec[u];
     }
   }
-  // ---- V: stage token-major (16-byte shared stores, conflict-free), read it back by column ---
-  {
-    const int tok = tid >> 4, part = tid & 15;
-    if (s_slot[tok] >= 0)
-      *reinterpret_cast<uint4 *>(&s_v[tok][part * kX]) = *reinterpret_cast<const uint4 *>(
-          value + (int64_t)(t0 + tok) * value_stride + h * kD + part * kX);
-  }
-  __syncthreads();
-  store_value_tile(s_slot, s_v, value_cache, num_kv_heads, h, tid);
+  store_value_tile<kT>(s_slot, s_v, value_cache, num_kv_heads, h, tid);
 }
 
 // Inverse traversal: cache -> packed key/value rows.
@@ -294,21 +307,30 @@ extern "C" char *aici_reshape_and_cache(const void *key, const void *value, void
   AICI_CHECK(((uintptr_t)key | (uintptr_t)value | (uintptr_t)key_cache |
               (uintptr_t)value_cache) % 16 == 0,
              "%s: tensors must be 16-byte aligned", fn);
+  if (char *e = check_on_current_device(fn, "key_cache", key_cache)) return e;
   unsigned int *st = status_ptr();
   AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
-  dim3 grid((num_tokens + kTok - 1) / kTok, num_kv_heads);
   const int64_t num_slots = num_blocks * kB;
   auto k = static_cast<const __nv_bfloat16 *>(key);
   auto v = static_cast<const __nv_bfloat16 *>(value);
   auto kc = static_cast<__nv_bfloat16 *>(key_cache);
   auto vc = static_cast<__nv_bfloat16 *>(value_cache);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (slot_is_int64)
-    reshape_and_cache_kernel<true><<<grid, kThreads, 0, s>>>(
-        k, v, kc, vc, slot_mapping, num_tokens, num_kv_heads, num_slots, key_stride, value_stride, st);
-  else
-    reshape_and_cache_kernel<false><<<grid, kThreads, 0, s>>>(
-        k, v, kc, vc, slot_mapping, num_tokens, num_kv_heads, num_slots, key_stride, value_stride, st);
+  // 32 tokens per CTA (twice the bytes in flight per thread) once that still leaves four CTAs per
+  // multiprocessor; smaller calls keep 16 tokens per CTA so that more of the GPU takes part
+  const bool wide = (int64_t)((num_tokens + 31) / 32) * num_kv_heads >= (int64_t)4 * sm_count();
+  const int tok = wide ? 32 : 16;
+  dim3 grid((num_tokens + tok - 1) / tok, num_kv_heads);
+#define AICI_RAC_LAUNCH(S64, T)                                                                     \
+  reshape_and_cache_kernel<S64, T><<<grid, kThreads, 0, s>>>(k, v, kc, vc, slot_mapping, num_tokens, \
+                                                             num_kv_heads, num_slots, key_stride,    \
+                                                             value_stride, st)
+  if (slot_is_int64) {
+    if (wide) AICI_RAC_LAUNCH(true, 32); else AICI_RAC_LAUNCH(true, 16);
+  } else {
+    if (wide) AICI_RAC_LAUNCH(false, 32); else AICI_RAC_LAUNCH(false, 16);
+  }
+#undef AICI_RAC_LAUNCH
   AICI_CUDA(cudaGetLastError());
   return nullptr;
 }
@@ -331,6 +353,7 @@ extern "C" char *aici_gather_cached_kv(void *key, void *value, const void *key_c
   AICI_CHECK(((uintptr_t)key | (uintptr_t)value | (uintptr_t)key_cache |
               (uintptr_t)value_cache) % 16 == 0,
              "%s: tensors must be 16-byte aligned", fn);
+  if (char *e = check_on_current_device(fn, "key_cache", key_cache)) return e;
   unsigned int *st = status_ptr();
   AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
   dim3 grid((num_tokens + kTok - 1) / kTok, num_kv_heads);
@@ -393,6 +416,9 @@ extern "C" char *aici_copy_blocks_host(const int64_t *key_cache_ptrs_host,
     AICI_CHECK(key_cache_ptrs_host[l] % 16 == 0 && value_cache_ptrs_host[l] % 16 == 0 &&
                    key_cache_ptrs_host[l] != 0 && value_cache_ptrs_host[l] != 0,
                "%s: layer %d cache base must be non-NULL and 16-byte aligned", fn, l);
+  if (char *e = check_on_current_device(fn, "layer 0 key cache",
+                                        reinterpret_cast<const void *>(key_cache_ptrs_host[0])))
+    return e;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   for (int l0 = 0; l0 < num_layers; l0 += kArgLayers) {
     const int nl = num_layers - l0 < kArgLayers ? num_layers - l0 : kArgLayers;
@@ -520,7 +546,7 @@ rotary_reshape_and_cache_kernel(const int64_t *__restrict__ positions, __nv_bflo
     }
   }
   __syncthreads();
-  store_value_tile(s_slot, s_v, value_cache, num_kv_heads, h, tid);
+  store_value_tile<kTok>(s_slot, s_v, value_cache, num_kv_heads, h, tid);
 }
 
 }  // namespace aici
@@ -552,6 +578,7 @@ extern "C" char *aici_rotary_reshape_and_cache(const int64_t *positions, void *q
   AICI_CHECK(((uintptr_t)query | (uintptr_t)key | (uintptr_t)value | (uintptr_t)cos_sin_cache |
               (uintptr_t)key_cache | (uintptr_t)value_cache) % 16 == 0,
              "%s: tensors must be 16-byte aligned", fn);
+  if (char *e = check_on_current_device(fn, "key_cache", key_cache)) return e;
   unsigned int *st = status_ptr();
   AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
   dim3 grid((num_tokens + kTok - 1) / kTok, num_kv_heads);

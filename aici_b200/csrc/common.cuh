@@ -9,6 +9,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "../../include/aici_b200.h"
 
 namespace aici {
@@ -35,9 +37,34 @@ inline char *err(const char *fmt, ...) {
       return ::aici::err("%s failed: %s", #call, cudaGetErrorString(e__));                 \
   } while (0)
 
-// Sticky status word, one per device (defined in status.cu).  Host code asks for its device
-// address once per device and hands it to every kernel as an argument.
+// Status block, one per device (defined in status.cu): word 0 holds the sticky status bits that
+// aici_last_status reads and clears; words 2-3 hold a 64-bit %globaltimer stamp of the most recent
+// pipeline time-out (see mbar_wait_abortable).  Host code asks for its device address once per
+// device and hands it to every kernel as an argument.
 unsigned int *status_ptr();
+
+// NULL when `ptr` is not device memory or lives on the current device; else an error string.
+char *check_on_current_device(const char *fn, const char *what, const void *ptr);
+
+// Multiprocessor count of the current device (cached per device; 148 if the query fails).
+int sm_count();
+
+// Runs `setup` once per device (the current one) under a lock; returns its error string, or NULL.
+// Used for cudaFuncSetAttribute and symbol-address look-ups that must happen before a first launch.
+struct OncePerDevice {
+  std::mutex mu;
+  bool done[64] = {false};
+  template <typename F>
+  char *run(F setup) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return strdup("no current CUDA device");
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[dev]) return nullptr;
+    if (char *e = setup()) return e;
+    done[dev] = true;
+    return nullptr;
+  }
+};
 
 __device__ __forceinline__ void set_status(unsigned int *st, unsigned int bits) {
   atomicOr(st, bits);
@@ -98,23 +125,56 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsign
   return true;
 }
 
-// Same, for kernels whose CTAs wait on each other's roles: also gives up as soon as any CTA
-// on the device has recorded a timeout, so one stuck pipeline cannot hold the grid for long.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Same, for kernels whose CTAs wait on each other's roles: also gives up when some CTA of the
+// device has timed out within the last two seconds, so that one stuck pipeline cannot hold a grid
+// of many waves for a second per wave.  The mark is a time stamp, not a sticky bit: it expires by
+// itself, so a time-out that was reported long ago (or a late peer in aici_peer_barrier, which
+// has its own status bit and leaves no stamp) never makes a later launch give up.
 __device__ __forceinline__ bool mbar_wait_abortable(uint64_t *bar, uint32_t parity,
                                                     unsigned int *st) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   unsigned polls = 0;
+  unsigned long long *stamp = reinterpret_cast<unsigned long long *>(st + 2);
   while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 255u) == 0u) {
-      if (*reinterpret_cast<volatile unsigned int *>(st) & AICI_STATUS_WAIT_TIMEOUT) return false;
+      const unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(stamp);
+      if (seen != 0ull && global_timer_ns() - seen < 2000000000ull) return false;
       if (clock64() - t0 > (1ll << 31)) {
         set_status(st, AICI_STATUS_WAIT_TIMEOUT);
+        atomicExch(stamp, global_timer_ns());
         return false;
       }
     }
   }
   return true;
+}
+
+// Barrier between the GPUs that share peer-mapped flag arrays, executed by the first `world` threads
+// of one warp: thread p publishes `epoch` into slot `rank` of rank p's array (release store at
+// system scope; the caller has fenced its own earlier stores) and waits, bounded to about a second,
+// until slot p of this rank's own array holds it.  A peer that never arrives is recorded as
+// AICI_STATUS_PEER_TIMEOUT and the thread returns.
+__device__ __forceinline__ void peer_signal_and_wait(unsigned int *const *flags, int rank, int p,
+                                                     unsigned int epoch, unsigned int *status) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags[p] + rank), "r"(epoch) : "memory");
+  const unsigned int *mine = flags[rank] + p;
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int)(v - epoch) >= 0) break;
+    if (clock64() - t0 > (1ll << 31)) {  // give up, report, keep the context usable
+      set_status(status, AICI_STATUS_PEER_TIMEOUT);
+      break;
+    }
+  }
 }
 
 // 1-D bulk copy global -> shared, completion counted on an mbarrier (TMA engine, no tensor

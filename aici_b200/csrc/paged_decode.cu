@@ -66,6 +66,9 @@ struct DecodeParams {
   int64_t q_stride, kv_block_stride, kv_head_stride;
   float scale_log2e;
   unsigned int *status;
+  // fused cross-GPU barrier in the merge kernel's tail (sync != 0): rank p's flag array
+  unsigned int *peer_flags[8];
+  int sync, rank;
 };
 
 struct Item {
@@ -523,19 +526,47 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const Dec
     *reinterpret_cast<float4 *>(&s_acc[warp][4 * lane]) = make_float4(a0, a1, a2, a3);
     if (lane == 0) s_w[warp] = wsum;
     __syncthreads();
-    if (tw != 0) return;
-    a0 = a1 = a2 = a3 = wsum = 0.f;
+    if (tw == 0) {
+      a0 = a1 = a2 = a3 = wsum = 0.f;
 #pragma unroll
-    for (int w = 0; w < kTeam; ++w) {
-      const float4 v = *reinterpret_cast<const float4 *>(&s_acc[team * kTeam + w][4 * lane]);
-      a0 += v.x; a1 += v.y; a2 += v.z; a3 += v.w;
-      wsum += s_w[team * kTeam + w];
+      for (int w = 0; w < kTeam; ++w) {
+        const float4 v = *reinterpret_cast<const float4 *>(&s_acc[team * kTeam + w][4 * lane]);
+        a0 += v.x; a1 += v.y; a2 += v.z; a3 += v.w;
+        wsum += s_w[team * kTeam + w];
+      }
     }
   }
-  if (work) {
+  if (work && tw == 0) {
     const float inv = __fdividef(1.f, wsum + 1e-6f);
     const uint2 packed = make_uint2(pack_bf16(a0 * inv, a1 * inv), pack_bf16(a2 * inv, a3 * inv));
     for (int w = 0; w < p.world; ++w) *reinterpret_cast<uint2 *>(p.out[w] + out_off) = packed;
+  }
+  if (p.sync) {
+    // Fused head-gather barrier: the rows of this call are in every rank's buffer once all CTAs of
+    // this grid are through (the decode grid before it has completed: griddepcontrol.wait above).
+    // CTAs count themselves off in slot 9 of this rank's flag array; the last one resets the count
+    // (so that the launch can be replayed), takes the next epoch from slot 8 and runs the barrier
+    // of aici_peer_barrier on the lanes of its first warp.  The grid ends when every peer has
+    // signalled (or after the bounded wait), so work queued behind it may read all heads.
+    __shared__ unsigned int s_epoch, s_last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned int *mine = p.peer_flags[p.rank];
+      unsigned int last = 0, epoch = 0;
+      __threadfence_system();  // cumulative: covers the stores of the whole CTA (ordered by the barrier above)
+      if (atomicAdd(mine + 9, 1u) == gridDim.x - 1) {
+        atomicExch(mine + 9, 0u);
+        epoch = mine[8] + 1;
+        mine[8] = epoch;
+        __threadfence_system();
+        last = 1;
+      }
+      s_epoch = epoch;
+      s_last = last;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x < p.world)
+      peer_signal_and_wait(p.peer_flags, p.rank, threadIdx.x, s_epoch, p.status);
   }
 }
 
@@ -584,29 +615,14 @@ __global__ void __launch_bounds__(1024) paged_plan_kernel(const DecodeParams p, 
 }
 
 // ---- host side -------------------------------------------------------------------------------
-static int g_chunk_override = 0;
-
-static int sm_count() {
-  static int cached[64] = {0};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
-
-// Tokens per work item of the fixed-chunk traversal (used when the tuning hook asks for it, for
-// batches too large to plan inside the kernel, and -- with 512 -- for the v2 calling convention).
+// Tokens per work item of the fixed-chunk traversal (used by aici_paged_attention_v1_chunked when it
+// is given no chunk size, for batches too large to plan inside the kernel, and -- with 512 -- for
+// the v2 calling convention).
 // 256 (16 cache blocks, 128 KB of K+V) keeps the partial-result traffic near 1 %; with few
 // (sequence, kv head) pairs per GPU coarse items leave some warps with one item more than
 // others, so the chunk is halved until the upper bound of the item count reaches 16 per resident
 // warp, down to 64 tokens.
 static int pick_chunk(int num_seqs, int num_kv_heads, int max_context_len) {
-  if (g_chunk_override > 0) return g_chunk_override;
   const int64_t warps = (int64_t)2 * sm_count() * kWarps;
   int chunk = 256;
   while (chunk > 64 &&
@@ -619,7 +635,7 @@ static int pick_chunk(int num_seqs, int num_kv_heads, int max_context_len) {
 // the in-kernel plan, hence the batch limit, and 32-bit tile indices.
 constexpr int kMinSpanTiles = 4;
 static bool use_spans(int num_seqs, int num_kv_heads, int max_context_len) {
-  return g_chunk_override == 0 && num_seqs <= kMaxInlineSeqs &&
+  return num_seqs <= kMaxInlineSeqs &&
          (int64_t)num_seqs * num_kv_heads * ((max_context_len + kB - 1) / kB + 1) < (1ll << 30);
 }
 
@@ -698,16 +714,15 @@ static char *check_decode_args(const char *fn, const void *out, const void *quer
 
 template <typename PartT, bool kSpans>
 static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaStream_t stream) {
-  static bool attr_set[64] = {false};
   const int smem = kWarps * kStages * kStageBytes + kWarps * kStages * (int)sizeof(uint64_t) +
                    (kMaxInlineSeqs + 1) * (int)sizeof(int);
-  int dev = 0;
-  AICI_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    AICI_CUDA(cudaFuncSetAttribute(paged_decode_kernel<PartT, kSpans>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set[dev] = true;
-  }
+  static OncePerDevice once;
+  if (char *e = once.run([&]() -> char * {
+        AICI_CUDA(cudaFuncSetAttribute(paged_decode_kernel<PartT, kSpans>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        return nullptr;
+      }))
+    return e;
   int grid = 2 * sm_count();
   if (kSpans) {
     p.inline_plan = 1;
@@ -763,15 +778,6 @@ static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaS
 
 using namespace aici;
 
-// Tuning hook for benchmarks: tokens per split chunk (multiple of 16, <= 512); 0 = default.
-extern "C" char *aici_tune_decode_chunk(int chunk_tokens) {
-  AICI_CHECK(chunk_tokens == 0 || (chunk_tokens % kB == 0 && chunk_tokens > 0 &&
-                                   chunk_tokens <= kMaxChunk),
-             "aici_tune_decode_chunk: chunk must be 0 or a multiple of 16 up to 512");
-  g_chunk_override = chunk_tokens;
-  return nullptr;
-}
-
 extern "C" size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads, int num_kv_heads,
                                                        int max_context_len) {
   if (num_seqs <= 0 || num_heads <= 0 || num_kv_heads <= 0) return kAlign;
@@ -781,6 +787,20 @@ extern "C" size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_hea
                           pick_chunk(num_seqs, num_kv_heads, max_context_len)).total;
 }
 
+static bool valid_chunk(int chunk_tokens) {
+  return chunk_tokens == 0 || (chunk_tokens > 0 && chunk_tokens % kB == 0 && chunk_tokens <= kMaxChunk);
+}
+
+extern "C" size_t aici_paged_attention_chunked_workspace_bytes(int num_seqs, int num_heads,
+                                                               int num_kv_heads, int max_context_len,
+                                                               int chunk_tokens) {
+  if (num_seqs <= 0 || num_heads <= 0 || num_kv_heads <= 0 || !valid_chunk(chunk_tokens)) return kAlign;
+  const int chunk = chunk_tokens > 0 ? chunk_tokens : pick_chunk(num_seqs, num_kv_heads, max_context_len);
+  return workspace_layout(num_seqs, num_heads, max_context_len, chunk).total;
+}
+
+// forced_chunk < 0: the default traversal; 0: the fixed-chunk traversal with its own chunk size;
+// > 0: the fixed-chunk traversal with that many tokens per chunk.
 static char *paged_attention_v1_impl(const char *fn, void *const *outs, int world, int out_heads,
                                      int out_head0, const void *query, const void *key_cache,
                                      const void *value_cache, int num_kv_heads, float scale,
@@ -789,7 +809,9 @@ static char *paged_attention_v1_impl(const char *fn, void *const *outs, int worl
                                      int num_seqs, int num_heads, int head_size,
                                      int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_stride,
                                      int64_t kv_block_stride, int64_t kv_head_stride, void *workspace,
-                                     size_t workspace_bytes, int dtype, aici_stream_t stream) {
+                                     size_t workspace_bytes, int dtype, aici_stream_t stream,
+                                     int forced_chunk = -1, void *const *peer_flags = nullptr,
+                                     int rank = 0) {
   void *out = outs[0];
   for (int w = 1; w < world; ++w)
     AICI_CHECK(outs[w] != nullptr && (uintptr_t)outs[w] % 16 == 0,
@@ -800,9 +822,12 @@ static char *paged_attention_v1_impl(const char *fn, void *const *outs, int worl
                                   max_num_blocks_per_seq, num_blocks, q_stride, kv_block_stride,
                                   kv_head_stride, dtype))
     return e;
+  if (char *e = check_on_current_device(fn, "query", query)) return e;
   if (num_seqs == 0) return nullptr;
-  const bool spans = use_spans(num_seqs, num_kv_heads, max_context_len);
-  const int chunk = spans ? kB : pick_chunk(num_seqs, num_kv_heads, max_context_len);
+  const bool spans = forced_chunk < 0 && use_spans(num_seqs, num_kv_heads, max_context_len);
+  const int chunk = spans ? kB
+                          : (forced_chunk > 0 ? forced_chunk
+                                              : pick_chunk(num_seqs, num_kv_heads, max_context_len));
   const WorkspaceLayout w = spans ? spans_layout(num_seqs, num_heads, num_kv_heads)
                                   : workspace_layout(num_seqs, num_heads, max_context_len, chunk);
   AICI_CHECK(workspace != nullptr && workspace_bytes >= w.total,
@@ -841,6 +866,10 @@ static char *paged_attention_v1_impl(const char *fn, void *const *outs, int worl
   p.kv_head_stride = kv_head_stride;
   p.scale_log2e = scale * kLog2e;
   p.status = st;
+  p.sync = peer_flags != nullptr && world > 1 ? 1 : 0;
+  p.rank = rank;
+  for (int i = 0; i < 8; ++i)
+    p.peer_flags[i] = static_cast<unsigned int *>(p.sync && i < world ? peer_flags[i] : nullptr);
   if (spans) return launch_decode<float, true>(p, nullptr, nullptr, static_cast<cudaStream_t>(stream));
   return launch_decode<float, false>(p, reinterpret_cast<int2 *>(ws + w.entries_off),
                                      reinterpret_cast<int *>(ws + w.n_entries_off),
@@ -889,6 +918,56 @@ extern "C" char *aici_paged_attention_v1_peers(void *const *outs, int world, int
                                  max_context_len, nullptr, num_seqs, num_heads, head_size,
                                  max_num_blocks_per_seq, num_blocks, q_stride, kv_block_stride,
                                  kv_head_stride, workspace, workspace_bytes, dtype, stream);
+}
+
+// The same call with the ranks' barrier folded into its last kernel: flag_ptrs are the flag arrays
+// of aici_peer_barrier (and the two may be mixed on the same arrays).  When this call's kernels have
+// finished, every rank's buffer holds all heads: no separate barrier launch follows.
+extern "C" char *aici_paged_attention_v1_peers_barrier(
+    void *const *outs, void *const *flag_ptrs, int world, int rank, int total_heads, int head0,
+    const void *query, const void *key_cache, const void *value_cache, int num_kv_heads, float scale,
+    const int32_t *block_tables, const int32_t *context_lens, int block_size, int max_context_len,
+    int num_seqs, int num_heads, int head_size, int max_num_blocks_per_seq, int64_t num_blocks,
+    int64_t q_stride, int64_t kv_block_stride, int64_t kv_head_stride, void *workspace,
+    size_t workspace_bytes, int dtype, aici_stream_t stream) {
+  const char *fn = "aici_paged_attention_v1_peers_barrier";
+  AICI_CHECK(outs != nullptr && flag_ptrs != nullptr && world >= 1 && world <= 8 && rank >= 0 && rank < world,
+             "%s: world must be 1..8 and rank inside it", fn);
+  AICI_CHECK(head0 >= 0 && num_heads > 0 && head0 + num_heads <= total_heads,
+             "%s: heads [%d, %d) do not fit %d total heads", fn, head0, head0 + num_heads, total_heads);
+  for (int i = 0; i < world; ++i)
+    AICI_CHECK(flag_ptrs[i] != nullptr && (uintptr_t)flag_ptrs[i] % 4 == 0,
+               "%s: flag array %d must be non-NULL and 4-byte aligned", fn, i);
+  if (char *e = paged_attention_v1_impl(fn, outs, world, total_heads, head0, query, key_cache, value_cache,
+                                        num_kv_heads, scale, block_tables, context_lens, block_size,
+                                        max_context_len, nullptr, num_seqs, num_heads, head_size,
+                                        max_num_blocks_per_seq, num_blocks, q_stride, kv_block_stride,
+                                        kv_head_stride, workspace, workspace_bytes, dtype, stream, -1,
+                                        flag_ptrs, rank))
+    return e;
+  // an empty batch launches nothing; the ranks still have to meet
+  if (num_seqs == 0) return aici_peer_barrier(flag_ptrs, world, rank, stream);
+  return nullptr;
+}
+
+// aici_paged_attention_v1 through the fixed-chunk traversal (every sequence cut into chunks of
+// chunk_tokens tokens, dealt out round-robin): kept so that tests and benchmarks can compare the two
+// traversals.  The chunk size is an argument of the call; nothing process-wide is changed.
+extern "C" char *aici_paged_attention_v1_chunked(
+    void *out, const void *query, const void *key_cache, const void *value_cache, int num_kv_heads,
+    float scale, const int32_t *block_tables, const int32_t *context_lens, int block_size,
+    int max_context_len, const float *alibi_slopes, int num_seqs, int num_heads, int head_size,
+    int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_stride, int64_t kv_block_stride,
+    int64_t kv_head_stride, void *workspace, size_t workspace_bytes, int chunk_tokens, int dtype,
+    aici_stream_t stream) {
+  const char *fn = "aici_paged_attention_v1_chunked";
+  AICI_CHECK(valid_chunk(chunk_tokens), "%s: chunk_tokens must be 0 or a multiple of 16 up to 512", fn);
+  void *outs[1] = {out};
+  return paged_attention_v1_impl(fn, outs, 1, num_heads, 0, query, key_cache, value_cache, num_kv_heads,
+                                 scale, block_tables, context_lens, block_size, max_context_len,
+                                 alibi_slopes, num_seqs, num_heads, head_size, max_num_blocks_per_seq,
+                                 num_blocks, q_stride, kv_block_stride, kv_head_stride, workspace,
+                                 workspace_bytes, dtype, stream, chunk_tokens);
 }
 
 extern "C" char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_logits,
@@ -943,6 +1022,9 @@ extern "C" char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_
   p.kv_head_stride = kv_head_stride;
   p.scale_log2e = scale * kLog2e;
   p.status = st;
+  p.sync = 0;
+  p.rank = 0;
+  for (int i = 0; i < 8; ++i) p.peer_flags[i] = nullptr;
   return launch_decode<__nv_bfloat16, false>(p, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 
@@ -966,7 +1048,7 @@ extern "C" char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_
 //   * the first call on each device looks the array's device address up (the name used in host
 //     code is only a handle, not an address a kernel could use) and sets a function attribute;
 //     make that first call outside any stream capture.
-constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB: 256 sequences x 32/8 heads need 7 MiB, 2048 x 32/8 do not fit
+constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB: 256 sequences x 32/8 heads need 6.4 MiB, 2048 x 32/8 do not fit
 static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
 
 extern "C" char *aici_paged_attention_v1_static(
@@ -977,16 +1059,25 @@ extern "C" char *aici_paged_attention_v1_static(
     int64_t kv_head_stride, int dtype, aici_stream_t stream) {
   const char *fn = "aici_paged_attention_v1_static";
   static void *scratch_addr[64] = {nullptr};
+  static OncePerDevice once;
   int dev = 0;
   AICI_CUDA(cudaGetDevice(&dev));
   AICI_CHECK(dev >= 0 && dev < 64, "%s: device index %d out of range", fn, dev);
-  if (scratch_addr[dev] == nullptr) {
-    void *p = nullptr;
-    AICI_CUDA(cudaGetSymbolAddress(&p, g_decode_scratch));
-    AICI_CHECK(p != nullptr, "%s: the scratch array has no device address", fn);
-    scratch_addr[dev] = p;
-  }
-  if (num_seqs > 0 && num_heads > 0) {
+  if (char *e = once.run([&]() -> char * {
+        void *p = nullptr;
+        AICI_CUDA(cudaGetSymbolAddress(&p, g_decode_scratch));
+        AICI_CHECK(p != nullptr, "%s: the scratch array has no device address", fn);
+        scratch_addr[dev] = p;
+        return nullptr;
+      }))
+    return e;
+  // argument errors first, so that a bad head count is not reported as a size problem
+  if (char *e = check_decode_args(fn, out, query, key_cache, value_cache, num_kv_heads, block_tables,
+                                  context_lens, block_size, max_context_len, alibi_slopes, num_seqs,
+                                  num_heads, head_size, max_num_blocks_per_seq, num_blocks, q_stride,
+                                  kv_block_stride, kv_head_stride, dtype))
+    return e;
+  if (num_seqs > 0) {
     const size_t need =
         aici_paged_attention_workspace_bytes(num_seqs, num_heads, num_kv_heads, max_context_len);
     AICI_CHECK(need <= kStaticScratchBytes,

@@ -27,18 +27,7 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerFlags f, int
   epoch = __shfl_sync(0xffffffffu, epoch, 0);
   if (p >= world) return;
   __threadfence_system();
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f.flags[p] + rank), "r"(epoch) : "memory");
-  const unsigned int *mine = f.flags[rank] + p;
-  const long long t0 = clock64();
-  for (;;) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-    if ((int)(v - epoch) >= 0) break;
-    if (clock64() - t0 > (1ll << 31)) {  // about a second: give up, report, keep the context usable
-      set_status(status, AICI_STATUS_WAIT_TIMEOUT);
-      break;
-    }
-  }
+  peer_signal_and_wait(f.flags, rank, p, epoch, status);
 }
 
 }  // namespace aici

@@ -3,18 +3,54 @@
 
 namespace aici {
 
-__device__ unsigned int g_status_word = 0;
+// [0] sticky status bits, [1] unused, [2..3] 64-bit time stamp of the latest pipeline time-out
+__device__ __align__(16) unsigned int g_status_words[4] = {0, 0, 0, 0};
+
+static std::mutex g_mu;
 
 unsigned int *status_ptr() {
   static unsigned int *cached[64] = {nullptr};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mu);
   if (cached[dev] == nullptr) {
     void *p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_words) != cudaSuccess) return nullptr;
     cached[dev] = static_cast<unsigned int *>(p);
   }
   return cached[dev];
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// Entry points work on the CURRENT device; a pointer that lives on another GPU would be
+// dereferenced by this device's SMs (a fault without peer access, a silent NVLink access with it).
+char *check_on_current_device(const char *fn, const char *what, const void *ptr) {
+  if (ptr == nullptr) return nullptr;
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;  // not a CUDA pointer the runtime knows: nothing to compare
+  }
+  if (attr.type != cudaMemoryTypeDevice) return nullptr;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return err("%s: no current CUDA device", fn);
+  if (attr.device != dev)
+    return err("%s: %s lives on GPU %d but the current device is %d (make the tensors' GPU current "
+               "before the call)", fn, what, attr.device, dev);
+  return nullptr;
 }
 
 }  // namespace aici

@@ -79,19 +79,6 @@ static char *classify(const char *fn, const char *what, const void *p, Place *pl
   return nullptr;
 }
 
-static int swap_sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
-      n = v;
-    else
-      return 148;
-  }
-  return n;
-}
-
 }  // namespace aici
 
 using namespace aici;
@@ -126,6 +113,14 @@ extern "C" char *aici_swap_blocks(const void *src, void *dst, const int64_t *blo
   AICI_CHECK(sp == kPlaceDevice || dp == kPlaceDevice, "%s: Invalid device combination", fn);
   AICI_CHECK(!(sp == kPlaceDevice && dp == kPlaceDevice) || sdev == ddev,
              "%s: src and dst must be on the same GPU", fn);
+  // The reference's cudaMemcpyAsync works from any current device; the copy kernel below runs on
+  // the current one, so the device-side cache has to live there.
+  int cur = -1;
+  AICI_CUDA(cudaGetDevice(&cur));
+  const int owner = sp == kPlaceDevice ? sdev : ddev;
+  AICI_CHECK(owner == cur,
+             "%s: the device cache lives on GPU %d but the current device is %d (make the cache's GPU "
+             "current before the call)", fn, owner, cur);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   if (sp == kPlacePageable || dp == kPlacePageable) {
@@ -156,7 +151,7 @@ extern "C" char *aici_swap_blocks(const void *src, void *dst, const int64_t *blo
       args.dst[p] = static_cast<int32_t>(block_mapping_host[2 * (p0 + p) + 1]);
     }
     const int64_t items = (int64_t)np * steps;
-    const int64_t cap = host_side ? kSwapCtasHost : (int64_t)8 * swap_sm_count();
+    const int64_t cap = host_side ? kSwapCtasHost : (int64_t)8 * sm_count();
     const int grid = static_cast<int>(items < cap ? items : cap);
     swap_blocks_kernel<<<grid, kSwapThreads, 0, st>>>(args, static_cast<const char *>(s_dev),
                                                       static_cast<char *>(const_cast<void *>(d_dev)),

@@ -148,11 +148,6 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   }
   if (tiles[0].rows == 0 && tiles[1].rows == 0) return;
   const int hk = tiles[1].rows > 0 ? tiles[1].h / p.group : tiles[0].h / p.group;
-  const bool stuck = (*reinterpret_cast<volatile unsigned int *>(p.status) & AICI_STATUS_WAIT_TIMEOUT) != 0;
-  if (stuck) {  // the device already reported a stuck pipeline: do not start another one
-    tiles[0].n_tiles = 0;
-    tiles[1].n_tiles = 0;
-  }
   // tiles that see no key at all are zero rows (flash_fwd_kernel.h:1056)
   if (tiles[0].rows > 0 && tiles[0].n_tiles == 0) zero_rows(p, q0, tiles[0], tid, kPrefillThreads);
   if (tiles[1].rows > 0 && tiles[1].n_tiles == 0) zero_rows(p, q0, tiles[1], tid, kPrefillThreads);
@@ -698,27 +693,89 @@ static char *make_tmap_nd(const char *fn, CUtensorMap *map, const void *base, in
   return nullptr;
 }
 
+// Encoded maps are kept in a small table keyed by everything that went into them (base address,
+// extents, strides, kind), guarded by a mutex: a serving loop calls with the same buffers step after
+// step, and an encode through the driver costs about as much as the launch itself.  A map depends
+// on nothing but its key, so an entry can never be stale; the oldest entry is overwritten when the
+// table is full.
+struct TmapKey {
+  const void *base;
+  int64_t a, b, c, d;
+  int kind;
+  bool operator==(const TmapKey &o) const {
+    return base == o.base && a == o.a && b == o.b && c == o.c && d == o.d && kind == o.kind;
+  }
+};
+constexpr int kTmapCacheSize = 64;
+struct TmapCache {
+  std::mutex mu;
+  TmapKey keys[kTmapCacheSize];
+  CUtensorMap maps[kTmapCacheSize];
+  int used = 0, next = 0;
+  bool find(const TmapKey &k, CUtensorMap *out) {
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; ++i)
+      if (keys[i] == k) {
+        *out = maps[i];
+        return true;
+      }
+    return false;
+  }
+  void put(const TmapKey &k, const CUtensorMap &m) {
+    std::lock_guard<std::mutex> lock(mu);
+    const int i = used < kTmapCacheSize ? used++ : (next++ % kTmapCacheSize);
+    keys[i] = k;
+    maps[i] = m;
+  }
+};
+static TmapCache g_tmap_cache;
+
 // [tokens, heads, 128] bf16 with element strides -> 3-D map, box = 64 (d) x 1 (head) x 128 (tokens).
 static char *make_tmap(const char *fn, CUtensorMap *map, const void *base, int64_t tokens, int heads,
                        int64_t tok_stride, int64_t head_stride) {
+  const TmapKey key = {base, tokens, heads, tok_stride, head_stride, 0};
+  if (g_tmap_cache.find(key, map)) return nullptr;
   cuuint64_t dims[3] = {(cuuint64_t)kHD, (cuuint64_t)heads, (cuuint64_t)tokens};
   cuuint64_t strides[2] = {(cuuint64_t)head_stride * 2, (cuuint64_t)tok_stride * 2};
   cuuint32_t box[3] = {64, 1, (cuuint32_t)kBM};
-  return make_tmap_nd(fn, map, base, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (char *e = make_tmap_nd(fn, map, base, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  g_tmap_cache.put(key, *map);
+  return nullptr;
+}
+
+// Paged caches: kind 1 = key cache (5-D, one half block per box), kind 2 = value cache (4-D, one
+// block per box, 32-byte swizzle).
+static char *make_cache_tmap(const char *fn, CUtensorMap *map, const void *base, bool value,
+                             int num_kv_heads, int64_t num_blocks, int64_t kv_head_stride,
+                             int64_t kv_block_stride) {
+  const TmapKey key = {base, num_kv_heads, num_blocks, kv_head_stride, kv_block_stride, value ? 2 : 1};
+  if (g_tmap_cache.find(key, map)) return nullptr;
+  if (!value) {  // [blk][h][c = 16][tok = 16][e = 8]: box = 8 tokens of all chunks
+    cuuint64_t dims[5] = {8, 16, 16, (cuuint64_t)num_kv_heads, (cuuint64_t)num_blocks};
+    cuuint64_t str[4] = {16, 256, (cuuint64_t)kv_head_stride * 2, (cuuint64_t)kv_block_stride * 2};
+    cuuint32_t box[5] = {8, 8, 16, 1, 1};
+    if (char *e = make_tmap_nd(fn, map, base, 5, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+  } else {  // [blk][h][d = 128][tok = 16]: box = one block, rows of 32 bytes
+    cuuint64_t dims[4] = {16, 128, (cuuint64_t)num_kv_heads, (cuuint64_t)num_blocks};
+    cuuint64_t str[3] = {32, (cuuint64_t)kv_head_stride * 2, (cuuint64_t)kv_block_stride * 2};
+    cuuint32_t box[4] = {16, 128, 1, 1};
+    if (char *e = make_tmap_nd(fn, map, base, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_32B)) return e;
+  }
+  g_tmap_cache.put(key, *map);
+  return nullptr;
 }
 
 template <bool kPaged>
 static char *launch_prefill(const char *fn, const CUtensorMap &tq, const CUtensorMap &tk,
                             const CUtensorMap &tv, const OutMaps &to, PrefillParams &p, int num_heads,
                             int batch, int max_seqlen_q, cudaStream_t stream) {
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  AICI_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    AICI_CUDA(cudaFuncSetAttribute(varlen_prefill_kernel<kPaged>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmemBytes));
-    attr_set[dev] = true;
-  }
+  static OncePerDevice once;
+  if (char *e = once.run([]() -> char * {
+        AICI_CUDA(cudaFuncSetAttribute(varlen_prefill_kernel<kPaged>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmemBytes));
+        return nullptr;
+      }))
+    return e;
   // two tiles per CTA: two heads of one kv group when the group is even, else two row tiles
   p.pair_heads = (p.group % 2 == 0) ? 1 : 0;
   const int mblocks = (max_seqlen_q + kBM - 1) / kBM;
@@ -766,6 +823,12 @@ static char *mha_varlen_fwd_impl(const char *fn, void *const *outs, int world, i
   for (int i = 0; i < 8; ++i)
     AICI_CHECK(strides[i] >= kHD && strides[i] % 8 == 0,
                "%s: token and head strides must be multiples of 8 elements and at least head_size", fn);
+  // this rank's heads must fit between two token rows of the output buffers
+  AICI_CHECK(o_head_stride > o_tok_stride ||
+                 (int64_t)(out_head0 + num_heads - 1) * o_head_stride + kHD <= o_tok_stride,
+             "%s: heads [%d, %d) do not fit an output row of %lld elements", fn, out_head0,
+             out_head0 + num_heads, (long long)o_tok_stride);
+  if (char *e = check_on_current_device(fn, "q", q)) return e;
   unsigned int *st = status_ptr();
   AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
 
@@ -795,12 +858,11 @@ static char *mha_varlen_fwd_impl(const char *fn, void *const *outs, int world, i
   p.max_blocks = 0;
   p.num_blocks = 0;
   // every output buffer gets a tensor map like the query's; this rank's heads start at out_head0
-  OutMaps to;
+  OutMaps to = {};
   p.total_q = total_q;
   p.tma_store = 1;
-  for (int w = 0; w < 8; ++w)
-    if (char *e = make_tmap(fn, &to.m[w], outs[w < world ? w : 0], total_q, out_head0 + num_heads, o_tok_stride,
-                            o_head_stride))
+  for (int w = 0; w < world; ++w)  // the kernel reads m[w] for w < world only
+    if (char *e = make_tmap(fn, &to.m[w], outs[w], total_q, out_head0 + num_heads, o_tok_stride, o_head_stride))
       return e;
   return launch_prefill<false>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q,
                                static_cast<cudaStream_t>(stream));
@@ -883,23 +945,16 @@ extern "C" char *aici_mha_varlen_paged_fwd(void *out, const void *q, const void 
   AICI_CHECK(kv_head_stride == kHD * 16 && kv_block_stride % 8 == 0 &&
                  kv_block_stride >= (int64_t)num_kv_heads * kHD * 16,
              "%s: cache must be [blocks, kv_heads, 128/8, 16, 8] with contiguous head tiles", fn);
+  if (char *e = check_on_current_device(fn, "q", q)) return e;
   unsigned int *st = status_ptr();
   AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
 
   CUtensorMap tq, tk, tv;
   if (char *e = make_tmap(fn, &tq, q, total_q, num_heads, q_tok_stride, q_head_stride)) return e;
-  {  // key cache [blk][h][c = 16][tok = 16][e = 8]: box = one half block (8 tokens of all chunks)
-    cuuint64_t dims[5] = {8, 16, 16, (cuuint64_t)num_kv_heads, (cuuint64_t)num_blocks};
-    cuuint64_t str[4] = {16, 256, (cuuint64_t)kv_head_stride * 2, (cuuint64_t)kv_block_stride * 2};
-    cuuint32_t box[5] = {8, 8, 16, 1, 1};
-    if (char *e = make_tmap_nd(fn, &tk, key_cache, 5, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
-  }
-  {  // value cache [blk][h][d = 128][tok = 16]: box = one block, rows of 32 bytes, 32-byte swizzle
-    cuuint64_t dims[4] = {16, 128, (cuuint64_t)num_kv_heads, (cuuint64_t)num_blocks};
-    cuuint64_t str[3] = {32, (cuuint64_t)kv_head_stride * 2, (cuuint64_t)kv_block_stride * 2};
-    cuuint32_t box[4] = {16, 128, 1, 1};
-    if (char *e = make_tmap_nd(fn, &tv, value_cache, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_32B)) return e;
-  }
+  if (char *e = make_cache_tmap(fn, &tk, key_cache, false, num_kv_heads, num_blocks, kv_head_stride, kv_block_stride))
+    return e;
+  if (char *e = make_cache_tmap(fn, &tv, value_cache, true, num_kv_heads, num_blocks, kv_head_stride, kv_block_stride))
+    return e;
   PrefillParams p;
   for (int i = 0; i < 8; ++i) p.out[i] = i == 0 ? static_cast<__nv_bfloat16 *>(out) : nullptr;
   p.world = 1;
@@ -917,11 +972,10 @@ extern "C" char *aici_mha_varlen_paged_fwd(void *out, const void *q, const void 
   p.max_blocks = max_num_blocks_per_seq;
   p.num_blocks = num_blocks;
   (void)max_context_len;
-  OutMaps to;
+  OutMaps to = {};
   p.total_q = total_q;
   p.tma_store = 1;
-  for (int w = 0; w < 8; ++w)
-    if (char *e = make_tmap(fn, &to.m[w], out, total_q, num_heads, o_tok_stride, o_head_stride)) return e;
+  if (char *e = make_tmap(fn, &to.m[0], out, total_q, num_heads, o_tok_stride, o_head_stride)) return e;
   return launch_prefill<true>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q,
                               static_cast<cudaStream_t>(stream));
 }

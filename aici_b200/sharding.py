@@ -9,18 +9,39 @@ writes, block copies, decode and prefill then need no communication at all (bloc
 and cu_seqlens are the same on every rank); afterwards every rank needs all heads of the
 attention output, which is one all-gather.
 
-torch.distributed is the plumbing (backend "nccl" on GPUs; "gloo" in the CPU tests).
+torch.distributed is the plumbing (backend "nccl" on GPUs; "gloo" in the CPU tests).  The
+peer-mapped buffers of the fused gather come from the library's own C ABI (CUDA IPC), not from
+torch: a host without libtorch maps them with the same four calls.
 """
-from typing import Optional
+import ctypes
+from typing import List, Optional
 
 import torch
 import torch.distributed as dist
 
-from .workloads import Shard
+from dataclasses import dataclass
 
 
 class ShardingError(RuntimeError):
     pass
+
+
+@dataclass
+class Shard:
+    """KV-head sharding: rank r of `world` owns kv heads [r*Hkv/world, (r+1)*Hkv/world) and the
+    matching query heads (the reference's get_num_heads_parallel, rllm-cuda/src/llm/config.rs:49-51)."""
+    rank: int = 0
+    world: int = 1
+
+    def kv_slice(self, num_kv_heads: int) -> slice:
+        if num_kv_heads % self.world != 0:
+            raise ShardingError("num_kv_heads must divide by the world size")
+        n = num_kv_heads // self.world
+        return slice(self.rank * n, (self.rank + 1) * n)
+
+    def q_slice(self, num_heads: int) -> slice:
+        n = num_heads // self.world
+        return slice(self.rank * n, (self.rank + 1) * n)
 
 
 def check_world(num_heads: int, num_kv_heads: int, world: int) -> None:
@@ -72,49 +93,182 @@ def gather_heads(out_local: torch.Tensor, group=None, buffer: Optional[torch.Ten
     return buffer.permute(1, 0, 2, 3).reshape(tokens, world * h_local, d)
 
 
-class PeerGather:
-    """Output buffer [rows, total_heads, head_size] allocated in symmetric memory on every rank of
-    `group` and mapped into every peer's address space (torch.distributed symmetric memory over
-    NVLink).  The attention entry points `*_peers` store each rank's heads straight into all of
-    these buffers; `barrier()` (a signal exchange on the current stream, with a timeout) is the only
-    synchronisation before `tensor` holds all heads on every rank."""
+def exchange_bytes(payload: bytes, group=None) -> List[bytes]:
+    """Every rank contributes `payload`; returns all ranks' payloads in rank order.  The channel is
+    the process group's object all-gather (any channel would do: the C ABI only needs the 64 handle
+    bytes to reach the other processes).  A rank that never joins makes the collective run into the
+    group's timeout; that, and any other failure, surfaces as ShardingError instead of a hang."""
+    if not dist.is_available() or not dist.is_initialized():
+        raise ShardingError("exchange_bytes needs an initialised process group")
+    world = dist.get_world_size(group)
+    out: List[Optional[bytes]] = [None] * world
+    try:
+        dist.all_gather_object(out, bytes(payload), group=group)
+    except Exception as e:  # noqa: BLE001 - timeouts and transport errors differ by backend
+        raise ShardingError("handle exchange failed (is every rank alive?): %s: %s"
+                            % (type(e).__name__, str(e)[:200])) from e
+    if any(not isinstance(x, (bytes, bytearray)) or len(x) != len(payload) for x in out):
+        raise ShardingError("handle exchange returned malformed entries")
+    return [bytes(x) for x in out]
 
-    def __init__(self, rows: int, total_heads: int, head_size: int, device, group=None,
-                 dtype=torch.bfloat16):
-        import torch.distributed._symmetric_memory as symm_mem
+
+class _DevicePointer:
+    """Lets torch view raw device memory (CUDA array interface, int16 elements)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes // 2,), "typestr": "<i2", "data": (int(ptr), False),
+                                         "version": 2}
+
+
+class PeerMemory:
+    """`nbytes` of zero-filled device memory on every rank of `group`, each rank's block mapped into
+    every other rank's process through the library's own calls (aici_peer_alloc / aici_peer_open:
+    CUDA IPC handles, exchanged with `exchange_bytes`).  ptrs[r] is rank r's block as THIS process
+    addresses it.  Set-up and tear-down only; never inside a step."""
+
+    def __init__(self, nbytes: int, device, group=None):
+        from . import _lib
         if not dist.is_initialized():
-            raise ShardingError("PeerGather needs an initialised process group")
+            raise ShardingError("PeerMemory needs an initialised process group")
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
-        if total_heads % self.world != 0:
-            raise ShardingError("%d heads do not divide over %d ranks" % (total_heads, self.world))
+        self.device = torch.device(device)
+        self.nbytes = int(nbytes)
+        self._lib = _lib
+        self._own = ctypes.c_void_p(0)
+        self._opened: List[int] = []
+        self.ptrs: List[int] = []
+        handle = (ctypes.c_ubyte * 64)()
+        err: Optional[str] = None
+        with torch.cuda.device(self.device):
+            try:
+                _lib.check("aici_peer_alloc", _lib.lib().aici_peer_alloc(
+                    ctypes.c_size_t(self.nbytes), ctypes.byref(self._own), handle))
+            except _lib.AiciError as e:
+                err = str(e)
+            # every rank takes part in the exchange even if its own allocation failed, so that
+            # nobody waits for a rank that has already given up
+            handles = exchange_bytes(bytes(handle) if err is None else b"\0" * 64, self.group)
+            if err is None and any(h == b"\0" * 64 for h in handles):
+                err = "another rank could not allocate its peer buffer"
+            if err is None:
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        self.ptrs.append(int(self._own.value))
+                        continue
+                    out = ctypes.c_void_p(0)
+                    try:
+                        _lib.check("aici_peer_open", _lib.lib().aici_peer_open(
+                            (ctypes.c_ubyte * 64).from_buffer_copy(h), ctypes.byref(out)))
+                    except _lib.AiciError as e:
+                        err = str(e)
+                        break
+                    self._opened.append(int(out.value))
+                    self.ptrs.append(int(out.value))
+            # agree on the outcome: one failed mapping anywhere means nobody uses the buffers
+            oks = exchange_bytes(b"\1" if err is None else b"\0", self.group)
+            if any(o != b"\1" for o in oks):
+                self.close(meet=False)
+                raise ShardingError(err or "another rank could not map the peer buffers")
+
+    def view(self, offset: int, shape, dtype=torch.bfloat16, rank: Optional[int] = None) -> torch.Tensor:
+        """A tensor over this rank's own block (or, with `rank`, over that rank's block as mapped here)."""
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        if offset % 16 or offset + nbytes > self.nbytes:
+            raise ShardingError("view outside the peer block")
+        base = self.ptrs[self.rank if rank is None else rank] + offset
+        t = torch.as_tensor(_DevicePointer(base, nbytes), device=self.device)
+        return t.view(dtype).view(*shape)
+
+    def close(self, meet: bool = True) -> None:
+        """Unmaps the peers' blocks, meets the other ranks, frees the own block (in that order: a
+        block must not be freed while a peer still has it mapped)."""
+        lib = self._lib.lib()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for p in self._opened:
+                lib.aici_peer_close(ctypes.c_void_p(p))
+            self._opened = []
+            if meet and dist.is_initialized():
+                try:
+                    dist.barrier(group=self.group)
+                except Exception:  # noqa: BLE001 - a dead peer must not keep this rank from freeing
+                    pass
+            if self._own.value:
+                lib.aici_peer_free(self._own)
+                self._own = ctypes.c_void_p(0)
+        self.ptrs = []
+
+
+class PeerGather:
+    """Output buffers [rows, total_heads, head_size] on every rank of `group`, mapped into every
+    peer's address space (PeerMemory), plus the flag array of the library's barrier.  The attention
+    entry points `*_peers` store each rank's heads straight into all ranks' buffers; `barrier()`
+    (bounded wait on the device) is the only synchronisation before `tensor` holds all heads.
+
+    There are `buffers` output buffers (default 2) used in turn: a peer may start its next step
+    while this rank still reads the current one, so consecutive steps write different buffers.
+    `flip()` moves on to the next buffer; with two buffers and one barrier per step, a buffer is
+    written again only after every rank has passed the barrier of the step in between, i.e. after
+    its readers (stream-ordered before that step's kernels) are done."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, rows: int, total_heads: int, head_size: int, device, group=None,
+                 dtype=torch.bfloat16, buffers: int = 2):
+        if not dist.is_initialized():
+            raise ShardingError("PeerGather needs an initialised process group")
+        grp = group if group is not None else dist.group.WORLD
+        world = dist.get_world_size(grp)
+        if total_heads % world != 0:
+            raise ShardingError("%d heads do not divide over %d ranks" % (total_heads, world))
+        if buffers < 1:
+            raise ShardingError("at least one buffer is needed")
         self.total_heads = total_heads
-        self.heads_per_rank = total_heads // self.world
-        self.tensor = symm_mem.empty((rows, total_heads, head_size), dtype=dtype, device=device)
-        self.handle = symm_mem.rendezvous(self.tensor, self.group)
-        self.ptrs = [int(x) for x in self.handle.buffer_ptrs]
-        if len(self.ptrs) != self.world or self.ptrs[self.rank] != self.tensor.data_ptr():
-            raise ShardingError("symmetric memory rendezvous returned unexpected buffer pointers")
-        # flags of the library's own barrier kernel: 16 slots per rank, zero, peer-mapped
-        self._flags = symm_mem.empty((16,), dtype=torch.int32, device=device)
-        self._flags.zero_()
-        self._flag_handle = symm_mem.rendezvous(self._flags, self.group)
-        self._flag_ptrs = [int(x) for x in self._flag_handle.buffer_ptrs]
-        torch.cuda.synchronize(device)
-        self.handle.barrier(channel=0, timeout_ms=60000)  # every rank's flags are zero before first use
+        self.heads_per_rank = total_heads // world
+        self.shape = (rows, total_heads, head_size)
+        elem = torch.empty((), dtype=dtype).element_size()
+        self._buf_bytes = (rows * total_heads * head_size * elem + 255) // 256 * 256
+        self.mem = PeerMemory(self.FLAG_BYTES + buffers * self._buf_bytes, device, grp)
+        self.group, self.world, self.rank = self.mem.group, self.mem.world, self.mem.rank
+        self.buffers = buffers
+        self.tensors = [self.mem.view(self.FLAG_BYTES + i * self._buf_bytes, self.shape, dtype)
+                        for i in range(buffers)]
+        self._ptrs = [[p + self.FLAG_BYTES + i * self._buf_bytes for p in self.mem.ptrs] for i in range(buffers)]
+        self.flag_ptrs = list(self.mem.ptrs)  # the first 16 words of each block, zero after allocation
+        self.cur = 0
+
+    @property
+    def tensor(self) -> torch.Tensor:
+        return self.tensors[self.cur]
+
+    @property
+    def ptrs(self) -> List[int]:
+        return self._ptrs[self.cur]
+
+    def flip(self) -> None:
+        self.cur = (self.cur + 1) % self.buffers
 
     @property
     def head0(self) -> int:
         return self.rank * self.heads_per_rank
 
+    def flag_array(self):
+        return (ctypes.c_void_p * self.world)(*[ctypes.c_void_p(x) for x in self.flag_ptrs])
+
     def barrier(self) -> None:
         """Enqueue the cross-rank barrier on the current stream (bounded wait on the device)."""
-        import ctypes
         from . import _lib
-        arr = (ctypes.c_void_p * self.world)(*[ctypes.c_void_p(x) for x in self._flag_ptrs])
-        dev = self.tensor.device
+        dev = self.mem.device
         with torch.cuda.device(dev):
-            res = _lib.lib().aici_peer_barrier(arr, ctypes.c_int(self.world), ctypes.c_int(self.rank),
+            res = _lib.lib().aici_peer_barrier(self.flag_array(), ctypes.c_int(self.world), ctypes.c_int(self.rank),
                                                ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
         _lib.check("peer_barrier", res)
+
+    def close(self) -> None:
+        self.tensors = []
+        self.mem.close()

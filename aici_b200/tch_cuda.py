@@ -361,6 +361,35 @@ def paged_attention_v1(out: torch.Tensor, query: torch.Tensor, key_cache: torch.
     _lib.check(fn, res)
 
 
+def paged_attention_v1_chunked(out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tensor,
+                               value_cache: torch.Tensor, num_kv_heads: int, scale: float,
+                               block_tables: torch.Tensor, context_lens: torch.Tensor, block_size: int,
+                               max_context_len: int, chunk_tokens: int) -> None:
+    """paged_attention_v1 through the fixed-chunk traversal with `chunk_tokens` tokens per chunk (0 =
+    the library's choice).  Test and benchmark hook: results match paged_attention_v1 up to the
+    rounding of different split points."""
+    fn = "paged_attention_v1_chunked"
+    dev, num_blocks, head_size = _decode_common(fn, out, query, key_cache, value_cache,
+                                                num_kv_heads, block_tables, context_lens, block_size)
+    num_seqs, num_heads, _ = query.shape
+    L = _lib.lib()
+    with _on_device(dev):
+        nbytes = L.aici_paged_attention_chunked_workspace_bytes(
+            ctypes.c_int(num_seqs), ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads),
+            ctypes.c_int(int(max_context_len)), ctypes.c_int(int(chunk_tokens)))
+        ws = _workspace(dev, nbytes)
+        res = L.aici_paged_attention_v1_chunked(
+            _p(out), _p(query), _p(key_cache), _p(value_cache), ctypes.c_int(num_kv_heads),
+            ctypes.c_float(scale), _p(block_tables), _p(context_lens), ctypes.c_int(block_size),
+            ctypes.c_int(int(max_context_len)), ctypes.c_void_p(0), ctypes.c_int(num_seqs),
+            ctypes.c_int(num_heads), ctypes.c_int(head_size), ctypes.c_int(block_tables.shape[1]),
+            ctypes.c_int64(num_blocks), ctypes.c_int64(query.stride(0)),
+            ctypes.c_int64(key_cache.stride(0)), ctypes.c_int64(key_cache.stride(1)),
+            _p(ws), ctypes.c_size_t(ws.numel()), ctypes.c_int(int(chunk_tokens)),
+            ctypes.c_int(_dtype(fn, query)), _stream(dev))
+    _lib.check(fn, res)
+
+
 def paged_attention_v2(out: torch.Tensor, exp_sums: torch.Tensor, max_logits: torch.Tensor,
                        tmp_out: torch.Tensor, query: torch.Tensor, key_cache: torch.Tensor,
                        value_cache: torch.Tensor, num_kv_heads: int, scale: float,
@@ -506,11 +535,13 @@ def rotary_embedding_reshape_and_cache(positions: torch.Tensor, query: torch.Ten
 def paged_attention_v1_peers(peer_ptrs: Sequence[int], total_heads: int, head0: int, query: torch.Tensor,
                              key_cache: torch.Tensor, value_cache: torch.Tensor, num_kv_heads: int,
                              scale: float, block_tables: torch.Tensor, context_lens: torch.Tensor,
-                             block_size: int, max_context_len: int) -> None:
+                             block_size: int, max_context_len: int,
+                             barrier_flags: Optional[Sequence[int]] = None, rank: int = 0) -> None:
     """paged_attention_v1 whose output rows go to head index head0 + h of the
     [num_seqs, total_heads, head_size] buffers at `peer_ptrs` (one device pointer per rank, this
     rank's own included; see aici_b200.sharding.PeerGather).  No collective follows; ranks
-    synchronise before reading."""
+    synchronise before reading -- with a barrier of their own, or, when `barrier_flags` (the ranks'
+    flag arrays) and `rank` are given, inside this call's last kernel."""
     fn = "paged_attention_v1_peers"
     dev = _require_cuda(fn, query, key_cache, value_cache, block_tables, context_lens)
     num_blocks, cache_kv_heads, head_size, cache_block = _cache_dims(fn, key_cache, value_cache)
@@ -530,14 +561,39 @@ def paged_attention_v1_peers(peer_ptrs: Sequence[int], total_heads: int, head0: 
             ctypes.c_int(num_seqs), ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads),
             ctypes.c_int(int(max_context_len)))
         ws = _workspace(dev, nbytes)
-        res = L.aici_paged_attention_v1_peers(
-            outs, ctypes.c_int(world), ctypes.c_int(total_heads), ctypes.c_int(head0), _p(query),
-            _p(key_cache), _p(value_cache), ctypes.c_int(num_kv_heads), ctypes.c_float(scale),
-            _p(block_tables), _p(context_lens), ctypes.c_int(block_size), ctypes.c_int(int(max_context_len)),
-            ctypes.c_int(num_seqs), ctypes.c_int(num_heads), ctypes.c_int(head_size),
-            ctypes.c_int(block_tables.shape[1]), ctypes.c_int64(num_blocks), ctypes.c_int64(query.stride(0)),
-            ctypes.c_int64(key_cache.stride(0)), ctypes.c_int64(key_cache.stride(1)), _p(ws),
-            ctypes.c_size_t(ws.numel()), ctypes.c_int(_dtype(fn, query)), _stream(dev))
+        tail = (_p(query), _p(key_cache), _p(value_cache), ctypes.c_int(num_kv_heads), ctypes.c_float(scale),
+                _p(block_tables), _p(context_lens), ctypes.c_int(block_size), ctypes.c_int(int(max_context_len)),
+                ctypes.c_int(num_seqs), ctypes.c_int(num_heads), ctypes.c_int(head_size),
+                ctypes.c_int(block_tables.shape[1]), ctypes.c_int64(num_blocks), ctypes.c_int64(query.stride(0)),
+                ctypes.c_int64(key_cache.stride(0)), ctypes.c_int64(key_cache.stride(1)), _p(ws),
+                ctypes.c_size_t(ws.numel()), ctypes.c_int(_dtype(fn, query)), _stream(dev))
+        if barrier_flags is None:
+            res = L.aici_paged_attention_v1_peers(outs, ctypes.c_int(world), ctypes.c_int(total_heads),
+                                                  ctypes.c_int(head0), *tail)
+        else:
+            if len(barrier_flags) != world:
+                raise AiciError("%s: one flag array per rank is needed" % fn)
+            flags = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in barrier_flags])
+            res = L.aici_paged_attention_v1_peers_barrier(outs, flags, ctypes.c_int(world), ctypes.c_int(rank),
+                                                          ctypes.c_int(total_heads), ctypes.c_int(head0), *tail)
+    _lib.check(fn, res)
+
+
+def gather_heads(peer_ptrs: Sequence[int], total_heads: int, head0: int, local: torch.Tensor) -> None:
+    """Stores local [rows, heads, 128] at head index head0 + h of every rank's
+    [rows, total_heads, 128] buffer in `peer_ptrs` (the head-output gather as a call of its own; a
+    barrier between the ranks has to follow before anyone reads)."""
+    fn = "gather_heads"
+    dev = _require_cuda(fn, local)
+    if local.dim() != 3 or local.stride(2) != 1 or local.stride(1) != local.shape[2]:
+        raise AiciError("%s: local must be [rows, heads, head_size] with contiguous heads" % fn)
+    world = len(peer_ptrs)
+    outs = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in peer_ptrs])
+    with _on_device(dev):
+        res = _lib.lib().aici_gather_heads(
+            outs, ctypes.c_int(world), ctypes.c_int(total_heads), ctypes.c_int(head0), _p(local),
+            ctypes.c_int64(local.shape[0]), ctypes.c_int(local.shape[1]), ctypes.c_int(local.shape[2]),
+            ctypes.c_int64(local.stride(0)), ctypes.c_int(_dtype(fn, local)), _stream(dev))
     _lib.check(fn, res)
 
 

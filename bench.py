@@ -7,15 +7,20 @@ One "step" is one decode step of the Llama-2-7B-shaped paged workload (batch 64,
 head size 128, block size 16, contexts uniform in [512, 4096], 16384-block pool): the cache
 write of the 64 new tokens (reshape_and_cache) followed by decode attention over the paged
 cache (paged_attention_v1).  With N > 1 the KV heads are split over the ranks (tensor-parallel
-layout) and the head outputs are all-gathered over NCCL inside the step, so the total work is
-fixed ("strong" scaling).  The metric is the achieved HBM traffic rate in TB/s computed from
+layout) and the head outputs are gathered inside the step (stored into every rank's buffer by the
+attention call itself, or all-gathered over NCCL with --gather nccl), so the total work is fixed
+("strong" scaling).  The metric is the achieved HBM traffic rate in TB/s computed from
 the ALGORITHMIC bytes of the step (K and V once per (sequence, kv head), q, out, block tables,
 context lengths, and the cache write), aggregated over all ranks.
 
 The line also carries the long-context causal prefill throughput (2 x 32768 tokens, 64 q / 8 kv
 heads) in TFLOP/s under "prefill", the roofline of the dominant decode kernel, an end-to-end
-figure through the public API with host buffers, and the CPU baseline: the PyTorch-CPU port of
-rLLM's own CPU kernels timed on a bounded sample of the same workload.
+figure through the public API with host buffers, device time and roofline fraction of the other
+configurations (GQA decode, the mixed step's decode, prefill chunks, cache write and fork copy)
+under "configs", the parity of every timed output against the CPU oracle on sampled rows (and, on
+more than one GPU, bit equality of the fused gather with an NCCL gather) under "parity" -- the run
+exits non-zero when a bound is exceeded -- and the CPU baseline: the PyTorch-CPU port of rLLM's own
+CPU kernels timed on the same workload.
 
 --impl reference times that CPU port (the reference's CPU path for this operation; its Rust
 original cannot be built in this image) with all host threads, on rank 0 only.
@@ -37,11 +42,19 @@ import torch  # noqa: E402
 METRIC = "paged-decode attn HBM TB/s (prefill attn TFLOPS under 'prefill')"
 UNIT = "TB/s"
 WORKLOAD = "decode_llama2_7b_b64_mha32_d128_bs16_ctx512-4096_pool16384+reshape_and_cache_64"
-CPU_SAMPLE_SEQS = 8
-# DRAM bytes (read + write) of paged_decode_kernel per algorithmic byte, from an ncu capture of
-# the 16-sequence case that `--profile decode` runs; traffic grows in proportion to the tokens
-# read, so the ratio carries over to the full launch.
-DECODE_TRAFFIC_RATIO = 1.011
+MAX_ABS, MEAN_ABS = 2e-2, 2e-3  # bf16 attention outputs against the fp32-softmax oracle
+L2_BYTES = 126 << 20
+# Bytes a GPU should stream before it meets the same cache line again, so that HBM and not L2 is
+# measured: when one step reads less than this per GPU (kv-head shards of 4 and 8 GPUs), the bench
+# keeps several copies of the KV pool and the steps walk through them in turn.
+MIN_STREAM_BYTES = 1 << 30
+# DRAM bytes (read + write) of paged_decode_kernel per algorithmic byte, from ncu captures of one
+# launch of rank 0's shard at each world size (`--profile decode --profile-world N`; the summaries
+# are under profiles/).  A world size without a capture reports no traffic figure.
+DECODE_TRAFFIC_RATIO = {1: 1.011}
+# DRAM bytes of one varlen_prefill_kernel launch of the 2 x 32768 problem per world size, scaled from
+# an ncu capture of the 2 x 4096 case by the number of (query tile, key tile) pairs; None = no capture.
+PREFILL_TRAFFIC_BYTES = {}
 
 
 def load_peaks():
@@ -52,6 +65,14 @@ def load_peaks():
                 "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
                 "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def shared_config(n_gpus, step_bytes):
+    """The part of the JSON line that names the workload: the same in both arms."""
+    return {"workload": WORKLOAD, "sharding": "kv-heads/%d" % n_gpus,
+            "algorithmic_bytes_per_step": int(step_bytes),
+            "l2": "inputs larger than L2: every step streams the K/V of all 64 sequences (2.4 GB over all "
+                  "GPUs); where a GPU's share is below 1 GB, consecutive steps read different copies of the pool"}
 
 
 class ClockSampler(threading.Thread):
@@ -115,12 +136,13 @@ def physical_gpu_index(local_rank):
 
 
 # ---------------------------------------------------------------------------------------------
-# CPU arm: the PyTorch-CPU port of rLLM's CPU kernels on a bounded sample of the workload
+# CPU arm: the PyTorch-CPU port of rLLM's CPU kernels on the same workload
 # ---------------------------------------------------------------------------------------------
-def cpu_sample_inputs(n_seqs):
-    """The first n_seqs sequences of the decode workload with their blocks compacted into a small
-    fp32 pool (the CPU build of rLLM runs fp32).  Contexts and tables are the benchmark's own."""
-    from aici_b200 import workloads
+def cpu_inputs(n_seqs=64):
+    """The decode workload's first n_seqs sequences (all 64 by default) with their blocks compacted
+    into an fp32 pool (the CPU build of rLLM runs fp32).  Contexts and tables are the benchmark's own;
+    the pool holds the blocks in use (the GPU arm's 16384-block pool is mostly free blocks)."""
+    import workloads
     ctx = workloads.draw_context_lens("uniform", 64, 512, 4096, 2001)[:n_seqs]
     hkv = hq = 32
     nblk = sum((c + 15) // 16 for c in ctx)
@@ -138,7 +160,7 @@ def cpu_sample_inputs(n_seqs):
     bt = sum((c + 15) // 16 for c in ctx) * 4 + 4 * n_seqs
     cw = n_seqs * hkv * 128 * 2 * 2 * 2
     return dict(q=q, kc=kc, vc=vc, table=table, ctx=torch.tensor(ctx, dtype=torch.int32), nk=nk, nv=nv,
-                slots=slots, hkv=hkv, bytes=kv + qo + bt + cw)
+                slots=slots, hkv=hkv, bytes=kv + qo + bt + cw, n_seqs=n_seqs)
 
 
 def cpu_step(c):
@@ -147,20 +169,21 @@ def cpu_step(c):
     return R.decode_step_cpu(c["q"], c["kc"], c["vc"], c["hkv"], 1.0 / 128 ** 0.5, c["table"], c["ctx"], 16)
 
 
-def time_cpu(steps, warmup):
+def time_cpu(steps, warmup, n_seqs=64):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    c = cpu_sample_inputs(CPU_SAMPLE_SEQS)
+    c = cpu_inputs(n_seqs)
     for _ in range(warmup):
         cpu_step(c)
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_step(c)
     dt = (time.perf_counter() - t0) / max(steps, 1)
+    what = "all 64 sequences" if n_seqs == 64 else "first %d of the 64 sequences" % n_seqs
     return {"value": c["bytes"] / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": "first %d of the 64 sequences (%.1f MB algorithmic), fp32, gather_cached_kv + "
-                      "repeat_kv + per-sequence scaled_dot_product_attention as in refkernels.rs, "
-                      "%.3f s per step" % (CPU_SAMPLE_SEQS, c["bytes"] / 1e6, dt)}, dt
+            "sample": "%s of the workload (%.1f MB algorithmic per step), %d timed steps, fp32, "
+                      "gather_cached_kv + repeat_kv + per-sequence scaled_dot_product_attention as in "
+                      "refkernels.rs, %.3f s per step" % (what, c["bytes"] / 1e6, steps, dt)}, dt, c["bytes"]
 
 
 def run_reference(args):
@@ -168,12 +191,14 @@ def run_reference(args):
     if rank != 0:
         return
     steps, warm = max(1, args.steps), max(1, args.warmup)
-    cb, dt = time_cpu(steps, warm)
+    cb, dt, step_bytes = time_cpu(steps, warm)
     line = {
         "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "CPU path of the reference (refkernels.rs port), bounded sample"},
+        "config": shared_config(args.gpus, step_bytes),
+        "note": "CPU path of the reference (refkernels.rs port; the Rust original cannot be built in this "
+                "image), whole workload per step, all host threads, rank 0 only",
         "cpu_baseline": cb,
         "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -181,161 +206,266 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------------------------
+# Parity checks (after the timed regions, never inside them): the CPU oracle as the checker
+# ---------------------------------------------------------------------------------------------
+def decode_parity(full, gathered, n_pick=8):
+    """Gathered decode output [S, Hq, 128] against the fp32-softmax oracle on the n_pick shortest and
+    n_pick longest sequences, all heads.  `full` is the UNSHARDED workload (same seed) on the GPU,
+    with the step's new tokens not yet written; their blocks are compacted onto the CPU, the new
+    tokens are written there by the oracle's reshape_and_cache, then the oracle attends."""
+    from oracle import cpu_oracle as O
+    ctx = full.context_list
+    order = sorted(range(len(ctx)), key=lambda i: ctx[i])
+    pick = order[:n_pick] + order[-n_pick:] if len(ctx) > 2 * n_pick else list(range(len(ctx)))
+    tables = full.block_tables.cpu()
+    rows = [tables[i, :(ctx[i] + 15) // 16].tolist() for i in pick]
+    flat = torch.tensor([b for r in rows for b in r], dtype=torch.int64, device=full.key_cache.device)
+    kc = full.key_cache[flat].cpu()
+    vc = full.value_cache[flat].cpu()
+    width = max(len(r) for r in rows)
+    bt = torch.zeros(len(pick), width, dtype=torch.int32)
+    pos, slots = 0, []
+    for j, r in enumerate(rows):
+        bt[j, :len(r)] = torch.arange(pos, pos + len(r), dtype=torch.int32)
+        c = ctx[pick[j]]
+        slots.append((pos + (c - 1) // 16) * 16 + (c - 1) % 16)
+        pos += len(r)
+    sel = torch.tensor(pick, dtype=torch.int64)
+    O.reshape_and_cache(full.new_key.cpu()[sel].contiguous(), full.new_value.cpu()[sel].contiguous(), kc, vc,
+                        torch.tensor(slots, dtype=torch.int32))
+    cl = torch.tensor([ctx[i] for i in pick], dtype=torch.int32)
+    want = O.paged_attention_v1(full.query.cpu()[sel].contiguous(), kc, vc, full.num_kv_heads, full.scale, bt, cl)
+    mx, mean = O.error_stats(gathered.cpu()[sel], want)
+    return [mx, mean], len(pick)
+
+
+def prefill_parity(full, gathered, n_rows=512, seed=77):
+    """Gathered prefill output [total_q, Hq, 128] against the oracle on n_rows random
+    (sequence, row, head) triples plus the first and last row of every sequence."""
+    from oracle import cpu_oracle as O
+    g = torch.Generator().manual_seed(seed)
+    hq = full.q.shape[1]
+    cu = full.cu_seqlens_q.cpu().tolist()
+    trip = []
+    for b in range(len(cu) - 1):
+        for t in (cu[b], cu[b + 1] - 1):
+            trip.append((b, t, int(torch.randint(0, hq, (1,), generator=g))))
+    while len(trip) < n_rows:
+        b = int(torch.randint(0, len(cu) - 1, (1,), generator=g))
+        t = int(torch.randint(cu[b], cu[b + 1], (1,), generator=g))
+        trip.append((b, t, int(torch.randint(0, hq, (1,), generator=g))))
+    rows = torch.tensor(trip, dtype=torch.int32)
+    want = O.flash_attn_varlen_rows(full.q.cpu(), full.k.cpu(), full.v.cpu(), full.cu_seqlens_q.cpu(),
+                                    full.cu_seqlens_k.cpu(), rows, full.scale, True)
+    idx_t = rows[:, 1].to(torch.int64).to(gathered.device)
+    idx_h = rows[:, 2].to(torch.int64).to(gathered.device)
+    got = gathered[idx_t, idx_h].cpu()
+    mx, mean = O.error_stats(got, want)
+    return [mx, mean], len(trip)
+
+
+# ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
-def run_ours(args):
-    import torch.distributed as dist
-    from aici_b200 import tch_cuda, workloads, _lib
+class Runner:
+    """Process-wide pieces of one bench run: device, ranks, peaks, timing helpers."""
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
+    def __init__(self, args):
+        import torch.distributed as dist
+        self.dist = dist
+        self.args = args
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != args.gpus and self.world == 1 and args.gpus > 1:
             raise SystemExit("launch with torch.distributed.run --nproc-per-node %d" % args.gpus)
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    peaks = load_peaks()
-    shard = workloads.Shard(rank=rank, world=world)
+        self.dev = torch.device("cuda", self.local_rank)
+        torch.cuda.set_device(self.dev)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.peaks = load_peaks()
+        import workloads
+        self.shard = workloads.Shard(rank=self.rank, world=self.world)
+        self.flush_buf = None
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(ms):
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    def max_over_ranks(self, x):
+        if self.world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item())
+
+    def all_true(self, ok):
+        if self.world == 1:
+            return bool(ok)
+        t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
+        return bool(int(t.item()))
+
+    def flush(self):
+        """Writes a buffer of four times the L2 size."""
+        if self.flush_buf is None:
+            self.flush_buf = torch.empty(4 * L2_BYTES, dtype=torch.uint8, device=self.dev)
+        self.flush_buf.zero_()
+
+    def capture(self, fn):
+        """fn's launches as a CUDA graph (one eager run first, on the capture stream, so that lazily
+        sized scratch exists before the capture)."""
+        side = torch.cuda.Stream(self.dev)
+        side.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream(self.dev).wait_stream(side)
+        self.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            fn()
+        return g
+
+    def time_flushed(self, fn, iters, warm=3, graph=True):
+        """Median device time (ms) of one launch of fn with the L2 flushed before it; max over ranks.
+        fn is replayed as a CUDA graph, so the figure does not depend on the host's launch speed."""
+        run = self.capture(fn).replay if graph else fn
+        ts = []
+        for i in range(warm + iters):
+            if self.world > 1:
+                self.dist.barrier()
+            self.flush()  # also gives the host time to queue the launch behind it
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            run()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                ts.append(a.elapsed_time(b))
+        return self.max_over_ranks(statistics.median(ts))
+
+
+def roof(kind, work_local, ms, peaks, extra=None):
+    if kind == "hbm":
+        ach, peak, unit = work_local / (ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+    else:
+        ach, peak, unit = work_local / (ms * 1e-3) / 1e12, peaks["bf16_tflops_sustained"], "TFLOP/s"
+    row = {"ms": ms, "bound": "hbm" if kind == "hbm" else "tensor", "achieved": ach, "unit": unit,
+           "peak": peak, "frac": ach / peak, "work_per_gpu": work_local}
+    if kind != "hbm":
+        row["frac_of_burst_peak"] = ach / peaks["bf16_tflops"]
+    if extra:
+        row.update(extra)
+    return row
+
+
+def run_ours(args):
+    from aici_b200 import tch_cuda, _lib, sharding
+    import workloads
+    R = Runner(args)
+    dist, dev, world, rank, peaks, shard = R.dist, R.dev, R.world, R.rank, R.peaks, R.shard
 
     # ---- decode workload ------------------------------------------------------------------
     w = workloads.decode_llama2_7b(dev, shard=shard)
     S, hq_local = w.query.shape[0], w.query.shape[1]
+    hq_total = hq_local * world
     out = torch.empty_like(w.query)
     gathered = torch.empty(world, S, hq_local, 128, dtype=torch.bfloat16, device=dev) if world > 1 else None
     step_bytes_local = w.algorithmic_bytes() + w.cache_write_bytes()
     decode_bytes_local = w.algorithmic_bytes()
+    # pools: copies of this rank's KV pool that consecutive steps read in turn (see MIN_STREAM_BYTES)
+    n_pools = 1
+    while n_pools * decode_bytes_local < MIN_STREAM_BYTES and n_pools < 8:
+        n_pools *= 2
+    pools = [(w.key_cache, w.value_cache)] + [(w.key_cache.clone(), w.value_cache.clone())
+                                              for _ in range(n_pools - 1)]
     fused = world > 1 and args.gather == "fused"
-    pg = None
-    fused_fallback = None
+    pg, fused_fallback = None, None
     if fused:
-        from aici_b200 import sharding
-        # peer-mapped buffers come from torch's symmetric-memory allocator; if any rank cannot set
-        # them up, every rank falls back to the NCCL gather (and the JSON line says so)
+        # peer-mapped output buffers through the library's own calls (CUDA IPC); if any rank cannot
+        # set them up, every rank falls back to the NCCL gather (and the JSON line says so)
         try:
-            pg = sharding.PeerGather(S, hq_local * world, 128, dev)
-            ok = 1
+            pg = sharding.PeerGather(S, hq_total, 128, dev, buffers=2)
+            pg.barrier()
         except Exception as e:  # noqa: BLE001
-            fused_fallback, ok = "%s: %s" % (type(e).__name__, str(e)[:120]), 0
-        flag = torch.tensor([ok], dtype=torch.int32, device=dev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
+            fused_fallback = "%s: %s" % (type(e).__name__, str(e)[:160])
             fused, pg = False, None
-            fused_fallback = fused_fallback or "another rank could not map peer memory"
-        else:
-            pg.barrier()
 
-    def attention(q, bt, cl):
-        """decode attention + head gather: fused epilogue (peer stores + barrier) or NCCL all-gather"""
+    def attention(q, bt, cl, pool, buf):
+        """decode attention + head gather: fused epilogue (peer stores, barrier folded into the last
+        kernel) into output buffer `buf`, or an NCCL all-gather"""
+        kc, vc = pools[pool]
         if fused:
-            tch_cuda.paged_attention_v1_peers(pg.ptrs, hq_local * world, pg.head0, q, w.key_cache, w.value_cache,
-                                              w.num_kv_heads, w.scale, bt, cl, 16, w.max_context_len)
-            pg.barrier()
-            return pg.tensor
-        tch_cuda.paged_attention_v1(out, q, w.key_cache, w.value_cache, w.num_kv_heads, w.scale, bt, cl, 16,
-                                    w.max_context_len, None)
+            tch_cuda.paged_attention_v1_peers(pg._ptrs[buf], hq_total, pg.head0, q, kc, vc, w.num_kv_heads,
+                                              w.scale, bt, cl, 16, w.max_context_len,
+                                              barrier_flags=pg.flag_ptrs, rank=pg.rank)
+            return pg.tensors[buf]
+        tch_cuda.paged_attention_v1(out, q, kc, vc, w.num_kv_heads, w.scale, bt, cl, 16, w.max_context_len, None)
         if world > 1:
             dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), out)
             return gathered
         return out
 
-    def step():
-        tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
-        attention(w.query, w.block_tables, w.context_lens)
+    def step(i=0):
+        kc, vc = pools[i % n_pools]
+        tch_cuda.reshape_and_cache(w.new_key, w.new_value, kc, vc, w.slot_mapping)
+        return attention(w.query, w.block_tables, w.context_lens, i % n_pools, i % 2)
 
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    sampler.start()
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # The step (cache write, decode, merge, cross-GPU barrier) is a handful of short launches, so
-    # it is captured once into a CUDA graph and replayed; the NCCL variant is launched eagerly.
+    # a graph per (pool, output buffer) combination; step i replays graph i mod n_graphs
+    n_graphs = max(n_pools, 2 if fused else 1)
     use_graph = (world == 1 or fused) and not args.no_graph
-    if use_graph:
-        side = torch.cuda.Stream(dev)
-        side.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(side):
-            step()  # sizes this stream's workspace outside the capture
-        torch.cuda.current_stream(dev).wait_stream(side)
-        barrier()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            step()
-        for _ in range(3):
-            graph.replay()
-        barrier()
+    sampler = ClockSampler(physical_gpu_index(R.local_rank))
+    sampler.start()
+    for i in range(args.warmup):
+        step(i)
+    R.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    prof = torch.cuda.cudart() if args.profile_step is not None else None
+
+    def timed_steps(runs, steps, profile=False):
+        """`steps` back-to-back steps between two events -> (device ms, host wall ms).  With
+        `profile`, one step is bracketed by the profiler API (cudaProfilerStart/Stop, as rLLM's
+        --profile-step does around one forward pass, so that a capture can be limited to it)."""
+        R.barrier()
+        t0 = time.perf_counter()
         ev0.record()
-        for _ in range(args.steps):
-            graph.replay()
+        for i in range(steps):
+            mark = profile and prof is not None and i == args.profile_step
+            if mark:
+                prof.cudaProfilerStart()
+            runs[i % len(runs)]()
+            if mark:
+                prof.cudaProfilerStop()
         ev1.record()
-        barrier()
-    else:
-        ev0.record()
-        for _ in range(args.steps):
-            step()
-        ev1.record()
-        barrier()
-    # The decode call alone (decode + merge launches; with the fused gather their stores to the
-    # peers), for the roofline: K back-to-back replays of a graph holding just that call, so the
-    # figure is device time and does not depend on how fast the host can launch (eager launches
-    # with per-step events when graphs are off).
-    def attention_only():
-        if fused:
-            tch_cuda.paged_attention_v1_peers(pg.ptrs, hq_local * world, pg.head0, w.query, w.key_cache,
-                                              w.value_cache, w.num_kv_heads, w.scale, w.block_tables,
-                                              w.context_lens, 16, w.max_context_len)
-        else:
-            tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
-                                        w.block_tables, w.context_lens, 16, w.max_context_len, None)
+        ev1.synchronize()
+        wall = (time.perf_counter() - t0) * 1e3
+        R.barrier()
+        return ev0.elapsed_time(ev1), wall
 
     if use_graph:
-        side.wait_stream(torch.cuda.current_stream(dev))
-        att_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(att_graph, stream=side):
-            attention_only()
-        for _ in range(3):
-            att_graph.replay()
-        barrier()
-        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ea.record()
-        for _ in range(args.steps):
-            att_graph.replay()
-        eb.record()
-        barrier()
-        att_local_ms = ea.elapsed_time(eb) / args.steps
+        graphs = [R.capture(lambda i=i: step(i)) for i in range(n_graphs)]
+        runs = [g.replay for g in graphs]
     else:
-        att_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-                  for _ in range(args.steps)]
-        for i in range(args.steps):
-            tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
-            att_ev[i][0].record()
-            attention_only()
-            att_ev[i][1].record()
-            if fused:
-                pg.barrier()
-            elif world > 1:
-                dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), out)
-        barrier()
-        att_local_ms = sum(a.elapsed_time(b) for a, b in att_ev) / args.steps
-    barrier()
-    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+        runs = [(lambda i=i: step(i)) for i in range(n_graphs)]
+    for i in range(3 * n_graphs):
+        runs[i % n_graphs]()
+    ms_total = R.max_over_ranks(timed_steps(runs, args.steps, profile=True)[0])
     ms_step = ms_total / args.steps
-    att_ms = max_over_ranks(att_local_ms)
+
+    # The decode call alone (decode + merge launches; with the fused gather their stores to the
+    # peers and the barrier in the merge kernel's tail), for the roofline: back-to-back replays of
+    # graphs holding just that call, so the figure is device time.
+    def attention_only(i=0):
+        return attention(w.query, w.block_tables, w.context_lens, i % n_pools, i % 2)
+
+    if use_graph:
+        a_runs = [R.capture(lambda i=i: attention_only(i)).replay for i in range(n_graphs)]
+    else:
+        a_runs = [(lambda i=i: attention_only(i)) for i in range(n_graphs)]
+    for i in range(3 * n_graphs):
+        a_runs[i % n_graphs]()
+    att_ms = R.max_over_ranks(timed_steps(a_runs, args.steps)[0]) / args.steps
     status = _lib.last_status()
     if status != 0:
         raise SystemExit("device status word is %d after the timed region" % status)
@@ -345,7 +475,7 @@ def run_ours(args):
     # ---- end to end through the public API with host buffers -------------------------------
     # The step's inputs (q, new k/v, slot map, block tables, context lens) sit in ONE page-locked
     # staging buffer at 256-byte aligned offsets and reach the device with ONE copy per step into a
-    # buffer of the same layout; the kernels read views of it.
+    # buffer of the same layout; the kernels read views of it; the gathered output is read back.
     parts = {"q": w.query, "nk": w.new_key, "nv": w.new_value, "slots": w.slot_mapping,
              "bt": w.block_tables, "cl": w.context_lens}
     offs, cur = {}, 0
@@ -362,50 +492,158 @@ def run_ours(args):
     for k, t in parts.items():
         section(staging, k).copy_(t.cpu())
     d = {k: section(dev_in, k) for k in parts}
-    host_out = torch.empty((S, hq_local * world, 128) if world > 1 else out.shape, dtype=out.dtype).pin_memory()
+    host_out = torch.empty((S, hq_total, 128) if world > 1 else out.shape, dtype=out.dtype).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in parts.values())
     d2h = host_out.numel() * host_out.element_size()
 
-    def e2e_step():
+    def e2e_step(i=0):
+        kc, vc = pools[i % n_pools]
         dev_in.copy_(staging, non_blocking=True)
-        tch_cuda.reshape_and_cache(d["nk"], d["nv"], w.key_cache, w.value_cache, d["slots"])
-        o = attention(d["q"], d["bt"], d["cl"])
+        tch_cuda.reshape_and_cache(d["nk"], d["nv"], kc, vc, d["slots"])
+        o = attention(d["q"], d["bt"], d["cl"], i % n_pools, i % 2)
         if world > 1 and not fused:
-            o = o.permute(1, 0, 2, 3).reshape(S, hq_local * world, 128)
+            o = o.permute(1, 0, 2, 3).reshape(S, hq_total, 128)
         host_out.copy_(o, non_blocking=True)
 
-    for _ in range(max(3, args.warmup // 2)):
-        e2e_step()
-    barrier()
-    e2e_run = e2e_step
+    for i in range(max(3, args.warmup // 2)):
+        e2e_step(i)
+    R.barrier()
     if use_graph:
-        # the whole step -- the copy in, the kernels, the copy out -- as one graph replay
-        side.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(side):
-            e2e_step()
-        torch.cuda.current_stream(dev).wait_stream(side)
-        barrier()
-        e2e_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(e2e_graph, stream=side):
-            e2e_step()
-        e2e_run = e2e_graph.replay
-        for _ in range(3):
-            e2e_run()
-        barrier()
-    t0 = time.perf_counter()
-    ev0.record()
-    for _ in range(args.steps):
-        e2e_run()
-    ev1.record()
-    barrier()
-    e2e_ms = max_over_ranks(max(ev0.elapsed_time(ev1), (time.perf_counter() - t0) * 1e3)) / args.steps
+        e_runs = [R.capture(lambda i=i: e2e_step(i)).replay for i in range(n_graphs)]
+    else:
+        e_runs = [(lambda i=i: e2e_step(i)) for i in range(n_graphs)]
+    for i in range(3 * n_graphs):
+        e_runs[i % n_graphs]()
+    e2e_dev_ms, e2e_wall = timed_steps(e_runs, args.steps)
+    e2e_ms = R.max_over_ranks(max(e2e_dev_ms, e2e_wall)) / args.steps  # the slower of device and host clocks
+    e2e_wall_ms = R.max_over_ranks(e2e_wall) / args.steps
     e2e_value = step_bytes_local * world / (e2e_ms * 1e-3) / 1e12
 
-    # ---- long-context causal prefill (2 x 32768, 64 q / 8 kv heads; heads split over ranks) ---
-    del w.key_cache, w.value_cache
+    # ---- parity of the timed decode step (outside the timed regions) --------------------------
+    parity = {}
+    last = step(0)
+    torch.cuda.synchronize()
+    dec_gathered = last if (world == 1 or fused) else last.permute(1, 0, 2, 3).reshape(S, hq_total, 128)
+    if world > 1:
+        # the fused gather against one NCCL gather of the same step, bit for bit, on every rank
+        tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                    w.block_tables, w.context_lens, 16, w.max_context_len, None)
+        via_nccl = sharding.gather_heads(out).contiguous()
+        same = torch.equal(dec_gathered.contiguous().view(torch.int16), via_nccl.view(torch.int16))
+        parity["fused_equals_nccl"] = R.all_true(same) if fused else None
+    dec_gathered = dec_gathered.clone()
+    del pools
+    w.key_cache = w.value_cache = None
     torch.cuda.empty_cache()
+    if rank == 0:
+        full = workloads.decode_llama2_7b(dev)
+        parity["decode"], parity["decode_sequences_checked"] = decode_parity(full, dec_gathered)
+        del full
+    torch.cuda.empty_cache()
+
+    # ---- the other configurations: device time per launch, L2 flushed before each -------------
+    configs = {}
+    cfg_iters = max(5, min(args.steps, 20))
+    if not args.headline_only:
+        for key, make in (("cfg3", workloads.decode_llama3_8b), ("cfg5_decode", workloads.decode_mixed_step)):
+            cw = make(dev, shard=shard)
+            o_loc = torch.empty_like(cw.query)
+            cpg = None
+            if fused:
+                cpg = sharding.PeerGather(cw.query.shape[0], cw.num_heads * world, 128, dev, buffers=1)
+                cpg.barrier()
+
+            def dec(cw=cw, o_loc=o_loc, cpg=cpg):
+                if cpg is not None:
+                    tch_cuda.paged_attention_v1_peers(cpg.ptrs, cw.num_heads * world, cpg.head0, cw.query,
+                                                      cw.key_cache, cw.value_cache, cw.num_kv_heads, cw.scale,
+                                                      cw.block_tables, cw.context_lens, 16, cw.max_context_len,
+                                                      barrier_flags=cpg.flag_ptrs, rank=cpg.rank)
+                else:
+                    tch_cuda.paged_attention_v1(o_loc, cw.query, cw.key_cache, cw.value_cache, cw.num_kv_heads,
+                                                cw.scale, cw.block_tables, cw.context_lens, 16,
+                                                cw.max_context_len, None)
+            tch_cuda.reshape_and_cache(cw.new_key, cw.new_value, cw.key_cache, cw.value_cache, cw.slot_mapping)
+            ms = R.time_flushed(dec, cfg_iters)
+            configs[key] = roof("hbm", cw.algorithmic_bytes(), ms, peaks,
+                                {"workload": cw.name, "includes": "decode + merge launches" +
+                                 (", peer stores and barrier" if cpg is not None else "")})
+            dec()
+            torch.cuda.synchronize()
+            g_out = (cpg.tensor if cpg is not None else
+                     (sharding.gather_heads(o_loc) if world > 1 else o_loc)).clone()
+            if cpg is not None:
+                cpg.close()
+            if key == "cfg5_decode":
+                # the AICI fork on this pool: 32 sequences x 4 children, last block each, 4 "layers"
+                rows_ = [cw.block_tables[i, :(c + 15) // 16].tolist() for i, c in enumerate(cw.context_list)]
+                used = set(b for r in rows_ for b in r)
+                free = [b for b in range(cw.key_cache.shape[0]) if b not in used]
+                mapping = workloads.fork_block_mapping(rows_, 32, 4, free)
+                flat = torch.tensor([x for s_, ds in mapping.items() for d_ in ds for x in (s_, d_)],
+                                    dtype=torch.int64)
+                layers = 4
+                kcs = [cw.key_cache] + [cw.key_cache.clone() for _ in range(layers - 1)]
+                vcs = [cw.value_cache] + [cw.value_cache.clone() for _ in range(layers - 1)]
+                ms = R.time_flushed(lambda: tch_cuda.copy_blocks(kcs, vcs, flat), cfg_iters)
+                blk_bytes = cw.num_kv_heads * 128 * 16 * 2
+                pairs = flat.numel() // 2
+                ok = True
+                for s_, ds in mapping.items():
+                    for d_ in ds:
+                        for l in range(layers):
+                            ok = ok and torch.equal(kcs[l][d_].view(torch.int16), kcs[l][s_].view(torch.int16)) \
+                                and torch.equal(vcs[l][d_].view(torch.int16), vcs[l][s_].view(torch.int16))
+                configs["cfg5_copy_blocks"] = roof(
+                    "hbm", pairs * layers * 2 * blk_bytes * 2, ms, peaks,
+                    {"workload": "fork of 32 sequences into 4 children, last block each: %d pairs x %d layers"
+                                 % (pairs, layers), "bit_exact": R.all_true(ok)})
+                del kcs, vcs
+            del cw.key_cache, cw.value_cache
+            torch.cuda.empty_cache()
+            if rank == 0:
+                full = make(dev)
+                parity[key], _ = decode_parity(full, g_out)
+                del full
+            torch.cuda.empty_cache()
+
+        # config 5, prefill part (8 chunks of 512) and the cache write of its 4288 tokens
+        pw5 = workloads.prefill_mixed_chunks(dev, shard=shard)
+        ms = R.time_flushed(lambda: tch_cuda.flash_attn_varlen(pw5.q, pw5.k, pw5.v, pw5.cu_seqlens_q,
+                                                               pw5.cu_seqlens_k, pw5.max_seqlen_q,
+                                                               pw5.max_seqlen_k, pw5.scale, True), cfg_iters)
+        configs["cfg5_prefill"] = roof("tensor", pw5.flops(), ms, peaks, {"workload": pw5.name})
+        o5 = tch_cuda.flash_attn_varlen(pw5.q, pw5.k, pw5.v, pw5.cu_seqlens_q, pw5.cu_seqlens_k,
+                                        pw5.max_seqlen_q, pw5.max_seqlen_k, pw5.scale, True)
+        g5 = sharding.gather_heads(o5) if world > 1 else o5
+        if rank == 0:
+            parity["cfg5_prefill"], _ = prefill_parity(workloads.prefill_mixed_chunks(dev), g5, n_rows=256)
+        hkv5 = pw5.k.shape[1]
+        n_tok = 4288
+        nb5 = n_tok // 16 + 8
+        kc5 = torch.zeros(nb5, hkv5, 16, 16, 8, dtype=torch.bfloat16, device=dev)
+        vc5 = torch.zeros(nb5, hkv5, 128, 16, dtype=torch.bfloat16, device=dev)
+        kk = torch.cat([pw5.k, pw5.k[:n_tok - pw5.k.shape[0]]]).contiguous()
+        vv = torch.cat([pw5.v, pw5.v[:n_tok - pw5.v.shape[0]]]).contiguous()
+        slots5 = torch.arange(n_tok, dtype=torch.int32, device=dev)
+        ms = R.time_flushed(lambda: tch_cuda.reshape_and_cache(kk, vv, kc5, vc5, slots5), cfg_iters)
+        ok = True
+        if rank == 0:
+            from oracle import cpu_oracle as O
+            kr, vr = torch.zeros_like(kc5).cpu(), torch.zeros_like(vc5).cpu()
+            O.reshape_and_cache(kk.cpu(), vv.cpu(), kr, vr, slots5.cpu())
+            ok = torch.equal(kc5.cpu().view(torch.int16), kr.view(torch.int16)) and \
+                torch.equal(vc5.cpu().view(torch.int16), vr.view(torch.int16))
+        configs["cfg5_reshape_and_cache"] = roof(
+            "hbm", n_tok * hkv5 * 128 * 2 * 2 * 2, ms, peaks,
+            {"workload": "4288 tokens (8 x 512 prefill + 192 decode), block-aligned chunks", "bit_exact": ok})
+        del pw5, kc5, vc5, kk, vv, o5, g5
+        torch.cuda.empty_cache()
+
+    # ---- long-context causal prefill (2 x 32768, 64 q / 8 kv heads; heads split over ranks) ---
     pw = workloads.prefill_long(dev, shard=shard)
     p_steps, p_warm = max(2, min(args.steps, 5)), 3
+    hq_p = pw.q.shape[1] * world
 
     def pstep():
         return tch_cuda.flash_attn_varlen(pw.q, pw.k, pw.v, pw.cu_seqlens_q, pw.cu_seqlens_k,
@@ -413,13 +651,12 @@ def run_ours(args):
 
     pbuf, ppg = None, None
     if fused:
-        ppg = sharding.PeerGather(pw.q.shape[0], pw.q.shape[1] * world, 128, dev)
+        ppg = sharding.PeerGather(pw.q.shape[0], hq_p, 128, dev, buffers=1)
         ppg.barrier()
 
         def pstep():  # noqa: F811
-            tch_cuda.flash_attn_varlen_peers(ppg.ptrs, pw.q.shape[1] * world, ppg.head0, pw.q, pw.k, pw.v,
-                                             pw.cu_seqlens_q, pw.cu_seqlens_k, pw.max_seqlen_q,
-                                             pw.max_seqlen_k, pw.scale, True)
+            tch_cuda.flash_attn_varlen_peers(ppg.ptrs, hq_p, ppg.head0, pw.q, pw.k, pw.v, pw.cu_seqlens_q,
+                                             pw.cu_seqlens_k, pw.max_seqlen_q, pw.max_seqlen_k, pw.scale, True)
             return ppg.tensor
     elif world > 1:
         pbuf = torch.empty(world, pw.q.shape[0], pw.q.shape[1], 128, dtype=torch.bfloat16, device=dev)
@@ -431,7 +668,7 @@ def run_ours(args):
             dist.all_gather_into_tensor(pbuf.view(-1, pbuf.shape[2], 128), o)
     for _ in range(p_warm):
         pgather(pstep())
-    barrier()
+    R.barrier()
     k_ms = []
     ev0.record()
     for _ in range(p_steps):
@@ -442,9 +679,9 @@ def run_ours(args):
         k_ms.append((a, b))
         pgather(o)
     ev1.record()
-    barrier()
-    p_ms = max_over_ranks(ev0.elapsed_time(ev1)) / p_steps
-    p_kernel_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in k_ms) / p_steps)
+    R.barrier()
+    p_ms = R.max_over_ranks(ev0.elapsed_time(ev1)) / p_steps
+    p_kernel_ms = R.max_over_ranks(sum(a.elapsed_time(b) for a, b in k_ms) / p_steps)
     clocks = sampler.stop()
     p_flops_local = pw.flops()
     p_tflops = p_flops_local * world / (p_ms * 1e-3) / 1e12
@@ -452,7 +689,39 @@ def run_ours(args):
     status = _lib.last_status()
     if status != 0:
         raise SystemExit("device status word is %d after the prefill region" % status)
+    # parity of the gathered prefill output
+    if fused:
+        p_gathered = o
+        local_o = tch_cuda.flash_attn_varlen(pw.q, pw.k, pw.v, pw.cu_seqlens_q, pw.cu_seqlens_k,
+                                             pw.max_seqlen_q, pw.max_seqlen_k, pw.scale, True)
+        via_nccl = sharding.gather_heads(local_o)
+        same = torch.equal(p_gathered.view(torch.int16), via_nccl.contiguous().view(torch.int16))
+        parity["prefill_fused_equals_nccl"] = R.all_true(same)
+        del local_o, via_nccl
+    elif world > 1:
+        p_gathered = pbuf.permute(1, 0, 2, 3).reshape(pw.q.shape[0], hq_p, 128)
+    else:
+        p_gathered = o
+    if rank == 0:
+        del pw
+        torch.cuda.empty_cache()
+        parity["prefill"], parity["prefill_rows_checked"] = prefill_parity(workloads.prefill_long(dev), p_gathered)
+    bad = []
+    for k_, v_ in parity.items():
+        if isinstance(v_, list) and (v_[0] > MAX_ABS or v_[1] > MEAN_ABS):
+            bad.append("%s max/mean abs error %.3e/%.3e" % (k_, v_[0], v_[1]))
+        if k_.endswith("equals_nccl") and v_ is False:
+            bad.append(k_ + " is false")
+    for k_, v_ in configs.items():
+        if v_.get("bit_exact") is False:
+            bad.append(k_ + " is not bit-exact")
+    parity["bounds"] = {"max_abs": MAX_ABS, "mean_abs": MEAN_ABS}
+    parity["ok"] = not bad
 
+    if pg is not None:
+        pg.close()
+    if ppg is not None:
+        ppg.close()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -460,49 +729,58 @@ def run_ours(args):
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
-        cpu_baseline, _ = time_cpu(steps=8, warmup=1)
+        cpu_baseline, _, _ = time_cpu(steps=4, warmup=1)
 
+    ratio = DECODE_TRAFFIC_RATIO.get(world)
+    config = shared_config(world, step_bytes_local * world)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {
-            "workload": WORKLOAD, "sharding": "kv-heads/%d" % world,
-            "l2": "no flush: each step streams %.2f GB of K/V per GPU, far above the 126 MB L2" % (
-                decode_bytes_local / 1e9),
-            "algorithmic_bytes_per_step": step_bytes_local * world,
+        "config": config,
+        "run": {
             "launch": "one CUDA-graph replay per step" if use_graph else "eager launches",
+            "pool_copies": n_pools,
+            "bytes_streamed_per_gpu_per_step": decode_bytes_local,
             "collective": ("none" if world == 1 else
-                           "fused: attention epilogue stores head outputs into every rank's buffer over "
-                           "NVLink (peer-mapped symmetric memory), then a signal barrier" if fused else
+                           "fused: the decode call stores head outputs into every rank's buffer over NVLink "
+                           "(buffers mapped with the library's CUDA-IPC calls, two used in turn) and its last "
+                           "kernel is the ranks' barrier" if fused else
                            "nccl all_gather of head outputs" +
                            (" (fused gather unavailable: %s)" % fused_fallback if fused_fallback else "")),
         },
         "roofline": {
-            "kernel": "paged_decode_kernel (+ plan and merge launches of the same call)",
+            "kernel": "paged_decode_kernel (+ the merge launch of the same call)",
             "bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": achieved_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
             "launch_ms": att_ms,
-            "traffic": DECODE_TRAFFIC_RATIO * decode_bytes_local,
-            "traffic_note": "ncu dram read+write of a 16-sequence launch, scaled by bytes",
+            "traffic": ratio * decode_bytes_local if ratio else None,
+            "traffic_note": ("ncu dram read+write of one launch of rank 0's shard at this world size, "
+                             "as a ratio to its algorithmic bytes" if ratio else
+                             "no ncu capture of this shard size on file"),
         },
-        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h,
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "host_wall_ms_per_step": e2e_wall_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "note": "q, new k/v, slot map, block tables, context lens copied from one pinned staging "
-                        "buffer (one copy) and the output read back every step; the KV cache is resident state"},
+                        "buffer (one copy) and the gathered output read back every step; the KV cache is "
+                        "resident state" + ("; steps alternate between two peer-mapped output buffers, so a "
+                                            "peer's next step never writes what this rank still reads"
+                                            if fused else "")},
         # this library's kernels inside the timed region, per step: reshape_and_cache, paged_decode,
-        # paged_merge, and the cross-GPU barrier kernel when the fused gather is used
-        "gpu_launches": (4 if fused else 3) * args.steps,
+        # paged_merge (whose tail is the cross-GPU barrier when the fused gather is used)
+        "gpu_launches": 3 * args.steps,
         "clocks": clocks,
+        "parity": parity,
+        "configs": configs,
         "prefill": {
-            "workload": pw.name + "_causal_d128", "tflops": p_tflops, "ms_per_step": p_ms, "steps": p_steps,
-            "flops_per_step": p_flops_local * world,
+            "workload": "prefill_2x32768_gqa64-8_causal_d128", "tflops": p_tflops, "ms_per_step": p_ms,
+            "steps": p_steps, "flops_per_step": p_flops_local * world,
             "roofline": {"kernel": "varlen_prefill_kernel", "bound": "tensor", "achieved": p_kernel_tflops,
                          "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                          "frac": p_kernel_tflops / peaks["bf16_tflops_sustained"],
                          "frac_of_burst_peak": p_kernel_tflops / peaks["bf16_tflops"],
                          "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "launch_ms": p_kernel_ms,
-                         "traffic": None},
+                         "traffic": PREFILL_TRAFFIC_BYTES.get(world)},
         },
     }
     if cpu_baseline is not None:
@@ -510,7 +788,8 @@ def run_ours(args):
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
-
+    if bad:
+        raise SystemExit("parity check failed: " + "; ".join(bad))
 
 
 # ---------------------------------------------------------------------------------------------
@@ -519,7 +798,8 @@ def run_ours(args):
 # ---------------------------------------------------------------------------------------------
 def run_suite(args):
     import torch.distributed as dist
-    from aici_b200 import tch_cuda, workloads, _lib
+    from aici_b200 import tch_cuda, _lib
+    import workloads
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -738,20 +1018,36 @@ def run_suite(args):
         dist.destroy_process_group()
 
 def run_profile_case(args):
-    """Small single-GPU cases for profiler captures (a few hundred MB, three launches): the
-    numbers printed here are not benchmark values."""
-    from aici_b200 import tch_cuda, workloads
+    """Small single-GPU cases for profiler captures (at most a few GB on the device, three launches):
+    the numbers printed here are not benchmark values.  `decode` with --profile-world N runs rank 0's
+    kv-head shard of an N-GPU run (all 64 sequences, 32 / N heads) -- the launch the scaling run
+    times at that N; without it, a 16-sequence case of the one-GPU shape."""
+    from aici_b200 import tch_cuda
+    import workloads
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     if args.profile == "decode":
-        w = workloads.decode_llama2_7b(dev, num_seqs=16, pool_blocks=4096)
+        if args.profile_world > 1:
+            w = workloads.decode_llama2_7b(dev, shard=workloads.Shard(0, args.profile_world))
+        else:
+            w = workloads.decode_llama2_7b(dev, num_seqs=16, pool_blocks=4096)
         out = torch.empty_like(w.query)
         for _ in range(3):
             tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
             tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
                                         w.block_tables, w.context_lens, 16, w.max_context_len, None)
         torch.cuda.synchronize()
-        print(json.dumps({"profile_case": "decode", "seqs": 16, "algorithmic_bytes": w.algorithmic_bytes()}))
+        print(json.dumps({"profile_case": "decode", "seqs": w.query.shape[0], "heads": w.num_heads,
+                          "algorithmic_bytes": w.algorithmic_bytes()}))
+    elif args.profile == "prefill_chunks":
+        pw = workloads.prefill_mixed_chunks(dev)
+        flush = torch.empty(4 * L2_BYTES, dtype=torch.uint8, device=dev)
+        for _ in range(3):
+            flush.zero_()
+            tch_cuda.flash_attn_varlen(pw.q, pw.k, pw.v, pw.cu_seqlens_q, pw.cu_seqlens_k, pw.max_seqlen_q,
+                                       pw.max_seqlen_k, pw.scale, True)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_case": "prefill_chunks", "flops": pw.flops()}))
     else:
         pw = workloads.prefill_long(dev, seqlen=4096)
         for _ in range(3):
@@ -771,10 +1067,17 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch the decode step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="multi-GPU head-output gather: fused into the attention epilogue (default) or NCCL")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="skip the per-configuration entries (configs 3 and 5) of the JSON line")
+    ap.add_argument("--profile-step", type=int, default=None,
+                    help="bracket this step of the timed region with cudaProfilerStart/Stop "
+                         "(what rLLM's --profile-step does), for captures limited to the profiler API range")
     ap.add_argument("--suite", action="store_true",
                     help="time all five configurations at the current world size and print one JSON object")
-    ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
+    ap.add_argument("--profile", default=None, choices=["decode", "prefill", "prefill_chunks"],
                     help="run a small case three times for a profiler capture and exit")
+    ap.add_argument("--profile-world", type=int, default=1,
+                    help="with --profile decode: run rank 0's shard of a run on this many GPUs")
     args = ap.parse_args()
     if args.profile:
         run_profile_case(args)

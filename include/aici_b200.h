@@ -15,6 +15,15 @@
  * KV-cache layout (rllm-cuda/src/llm/paged/cache_engine.rs:81-108), x = 16 / sizeof(T) = 8:
  *   key_cache   [num_blocks, num_kv_heads, head_size / x, block_size, x]
  *   value_cache [num_blocks, num_kv_heads, head_size, block_size]
+ *
+ * Current device: every entry point launches on the CURRENT CUDA device of the calling thread, and
+ * the tensors it is given must live there (outputs of other ranks in the `*_peers` calls excepted).
+ * The reference's wrappers inherit this from libtorch's device guard; a caller of this C ABI makes
+ * the tensors' GPU current itself (cudaSetDevice).  A mismatch is refused with an error string.
+ *
+ * Threads: the entry points are re-entrant.  The library keeps no mutable state a caller can
+ * observe, apart from the device status word below, per-device one-time set-up done under a lock,
+ * and a mutex-guarded table of encoded tensor maps keyed by (address, shape, strides).
  */
 #ifndef AICI_B200_H_
 #define AICI_B200_H_
@@ -35,14 +44,19 @@ enum {
   AICI_STATUS_OK = 0,
   AICI_STATUS_BAD_BLOCK = 1,   /* a block-table entry was outside [0, num_blocks)        */
   AICI_STATUS_BAD_SLOT = 2,    /* a slot index was outside the cache                      */
-  AICI_STATUS_WAIT_TIMEOUT = 4 /* a bounded wait on a shared-memory barrier gave up       */
+  AICI_STATUS_WAIT_TIMEOUT = 4, /* a bounded wait on a shared-memory barrier gave up      */
+  AICI_STATUS_PEER_TIMEOUT = 8  /* a peer GPU did not reach a barrier within its bounded wait */
 };
 
 /* Library version string (static storage). */
 const char *aici_version(void);
 
 /* Reads and clears the sticky status word of the current device (synchronises the
- * device).  Kernels never trap: an out-of-range block or slot is skipped and recorded. */
+ * device).  Kernels never trap: an out-of-range block or slot is skipped and recorded, and a wait
+ * that ran out is recorded and abandoned, so the result of THAT launch is incomplete while later
+ * launches run normally (no kernel reads the sticky bits).  A serving loop therefore polls this word
+ * where it synchronises anyway (once per step, or every few steps) and treats a non-zero value as
+ * the failure of the steps since the last poll. */
 char *aici_last_status(int *status_out);
 
 /* ---- KV-cache operations (bit-exact) ------------------------------------------------ */
@@ -102,17 +116,9 @@ char *aici_rotary_reshape_and_cache(const int64_t *positions, void *query, void 
 
 /* ---- decode attention over the paged cache ----------------------------------------- */
 
-/* Tuning hook for benchmarks and tests.  By default aici_paged_attention_v1 gives every warp of
- * its grid one run of consecutive 16-token tiles of the whole batch (even load whatever the
- * context lengths are).  A non-zero value (a multiple of 16 up to 512) selects the other
- * traversal instead: every sequence is cut into chunks of that many tokens, dealt out round-robin.
- * 0 restores the default.  Process-wide; changes what aici_paged_attention_workspace_bytes
- * returns. */
-char *aici_tune_decode_chunk(int chunk_tokens);
-
 /* Bytes of caller-owned scratch aici_paged_attention_v1 needs for these sizes: about 520 bytes
- * per query head of a group and (warp of the grid + sequence x kv head) for the default
- * traversal; per (sequence, head, chunk) for the chunked one. */
+ * per query head of a group and (warp of the grid + sequence x kv head); for batches above 2048
+ * sequences per (sequence, head, chunk).  Depends on its arguments and the device only. */
 size_t aici_paged_attention_workspace_bytes(int num_seqs, int num_heads, int num_kv_heads,
                                             int max_context_len);
 
@@ -133,6 +139,23 @@ char *aici_paged_attention_v1(void *out, const void *query, const void *key_cach
                               int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_stride,
                               int64_t kv_block_stride, int64_t kv_head_stride, void *workspace,
                               size_t workspace_bytes, int dtype, aici_stream_t stream);
+
+/* Test and benchmark hook (no counterpart in the reference): aici_paged_attention_v1 through the
+ * other traversal -- every sequence cut into chunks of chunk_tokens tokens (a multiple of 16 up to
+ * 512; 0 = the library's own choice), dealt out round-robin -- so that the two can be compared.
+ * The chunk size is an argument of the call; its workspace size comes from
+ * aici_paged_attention_chunked_workspace_bytes with the same chunk_tokens. */
+size_t aici_paged_attention_chunked_workspace_bytes(int num_seqs, int num_heads, int num_kv_heads,
+                                                    int max_context_len, int chunk_tokens);
+char *aici_paged_attention_v1_chunked(void *out, const void *query, const void *key_cache,
+                                      const void *value_cache, int num_kv_heads, float scale,
+                                      const int32_t *block_tables, const int32_t *context_lens,
+                                      int block_size, int max_context_len, const float *alibi_slopes,
+                                      int num_seqs, int num_heads, int head_size,
+                                      int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_stride,
+                                      int64_t kv_block_stride, int64_t kv_head_stride, void *workspace,
+                                      size_t workspace_bytes, int chunk_tokens, int dtype,
+                                      aici_stream_t stream);
 
 /* Replaces paged_attention_v2_C (lib.rs:122-137; vllm_bindings.cpp:31-45;
  * attention_kernels.cu:729-874).  Partition size 512 as in the reference (:733);
@@ -156,8 +179,8 @@ char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_logits, voi
  * allocate device memory at call time -- a serving loop that gave all spare memory to the KV
  * pool, or a binding without a device allocator -- and it calls no allocation routine itself.
  * Batches whose workspace (aici_paged_attention_workspace_bytes) exceeds 32 MiB are refused with
- * an error string.  All calls on one device share the array: calls that overlap on the GPU race,
- * so keep them on one stream.  The first call on a device looks up the array's address; make it
+ * an error string (argument errors are reported first).  All calls on one device share the array:
+ * calls that overlap on the GPU race, so keep them on one stream.  The first call on a device looks up the array's address; make it
  * outside any stream capture. */
 char *aici_paged_attention_v1_static(void *out, const void *query, const void *key_cache,
                                      const void *value_cache, int num_kv_heads, float scale,
@@ -219,8 +242,48 @@ char *aici_mha_varlen_fwd_peers(void *const *outs, int world, int head0, const v
  * first call; every rank must call it the same number of times (the epoch is a counter kept in the
  * array, so a captured launch can be replayed).  Enqueued on `stream`: work queued after it starts
  * once every rank's earlier work on its own stream has finished.  The wait is bounded (about a
- * second), then AICI_STATUS_WAIT_TIMEOUT is recorded. */
+ * second), then AICI_STATUS_PEER_TIMEOUT is recorded and the kernel returns. */
 char *aici_peer_barrier(void *const *flag_ptrs, int world, int rank, aici_stream_t stream);
+
+/* aici_paged_attention_v1_peers with that barrier folded into its last kernel: when the call's
+ * kernels have finished, every rank's buffer holds all heads, and no barrier launch follows (one
+ * launch less per decode step).  flag_ptrs as for aici_peer_barrier; the two may be mixed on the
+ * same arrays as long as all ranks make the same sequence of calls. */
+char *aici_paged_attention_v1_peers_barrier(void *const *outs, void *const *flag_ptrs, int world,
+                                            int rank, int total_heads, int head0, const void *query,
+                                            const void *key_cache, const void *value_cache,
+                                            int num_kv_heads, float scale, const int32_t *block_tables,
+                                            const int32_t *context_lens, int block_size,
+                                            int max_context_len, int num_seqs, int num_heads,
+                                            int head_size, int max_num_blocks_per_seq,
+                                            int64_t num_blocks, int64_t q_stride,
+                                            int64_t kv_block_stride, int64_t kv_head_stride,
+                                            void *workspace, size_t workspace_bytes, int dtype,
+                                            aici_stream_t stream);
+
+/* Peer-mapped device memory without libtorch or NCCL (no counterpart in the reference, which is
+ * single-GPU; the hook this serves is the per-rank kv-head count of
+ * rllm-cuda/src/llm/config.rs:30-36, 49-51).  One process per GPU:
+ *   owner : aici_peer_alloc(bytes, &ptr, handle)  -- cudaMalloc, zero-filled, 64-byte IPC handle
+ *   caller: moves the handle bytes to the other processes over any channel it has
+ *   peers : aici_peer_open(handle, &ptr)          -- maps the owner's buffer, peer access enabled
+ * The pointers go into outs[] / flag_ptrs[] above (index = owner's rank; a rank's own buffer is the
+ * pointer aici_peer_alloc gave it).  Tear-down: every peer aici_peer_close()s its mappings, the
+ * processes meet (the caller's own barrier), then each owner aici_peer_free()s.  These four calls
+ * allocate or map memory and synchronise the device: set-up time only, never inside a step. */
+#define AICI_PEER_HANDLE_BYTES 64
+char *aici_peer_alloc(size_t bytes, void **ptr_out, void *handle_out);
+char *aici_peer_open(const void *handle, void **ptr_out);
+char *aici_peer_close(void *ptr);
+char *aici_peer_free(void *ptr);
+
+/* The head-output gather as a call of its own, for attention results computed without the fused
+ * epilogue: local [rows, num_heads, 128] (row stride in elements) is stored at head index
+ * head0 + h of every rank's [rows, total_heads, 128] buffer (outs[0..world), peer-mapped, own
+ * included) with 16-byte stores over NVLink.  Follow it with aici_peer_barrier before reading. */
+char *aici_gather_heads(void *const *outs, int world, int total_heads, int head0, const void *local,
+                        int64_t rows, int num_heads, int head_size, int64_t local_row_stride,
+                        int dtype, aici_stream_t stream);
 
 /* Variable-length causal prefill that reads keys and values straight from the paged cache.
  * Replaces the sequence gather_cached_kv -> repeat_kv -> flash_attn_varlen of

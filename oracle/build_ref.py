@@ -31,7 +31,8 @@ def build(force: bool = False):
             os.path.join(kdir, "vllm", "attention", "attention_kernels.cu")]
     if not all(os.path.exists(s) for s in srcs):
         return None
-    if os.path.exists(OUT) and not force:
+    shim = os.path.join(HERE, "ref_shim.cpp")
+    if os.path.exists(OUT) and not force and os.path.getmtime(OUT) >= os.path.getmtime(shim):
         return OUT
     import torch
     from torch.utils import cpp_extension
@@ -47,6 +48,8 @@ def build(force: bool = False):
     for s in srcs + [os.path.join(HERE, "ref_shim.cpp")]:
         o = os.path.join(OUT_DIR, os.path.basename(s).rsplit(".", 1)[0] + ".o")
         objs.append(o)
+        if os.path.exists(o) and os.path.getmtime(o) >= os.path.getmtime(s):
+            continue  # left over from an interrupted build of the same source
         cmd = ["nvcc", *common, "-x", "cu", "-c", s, "-o", o]
         procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for s, pr in procs:

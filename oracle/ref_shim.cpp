@@ -9,12 +9,14 @@
 #include <torch/all.h>
 
 #include <cstring>
+#include <map>
 #include <string>
 
 #include "vllm/cache.h"
 #include "vllm/ops.h"
 
 namespace {
+using BlockMap = std::map<int64_t, int64_t>;  // named here: a comma inside REF_PROTECT would split its argument
 torch::Tensor wrap(void *p, std::vector<int64_t> sizes, torch::ScalarType t, int dev) {
   return torch::from_blob(p, sizes, torch::TensorOptions().dtype(t).device(torch::kCUDA, dev));
 }
@@ -62,6 +64,25 @@ char *ref_copy_blocks_2(void *kptrs, void *vptrs, void *mapping, int64_t layers,
     auto m = wrap(mapping, {2 * pairs}, torch::kInt64, dev);
     auto k0 = wrap(key0, {nblk, hkv, d / 8, bs, 8}, torch::kBFloat16, dev);
     copy_blocks_2(kp, vp, m, k0);
+  })
+}
+
+// swap_blocks of the reference (vllm/cache_kernels.cu:12-50).  src_dev / dst_dev: device index of
+// the tensor, or -1 for host memory (page-locked or not: the reference treats both as "cpu").
+// pairs: 2 * num_pairs int64 on the host, (src, dst, ...); sources are unique, as in the
+// reference's std::map.
+char *ref_swap_blocks(void *src, int src_dev, void *dst, int dst_dev, const int64_t *pairs, int64_t num_pairs,
+                      int64_t src_blocks, int64_t dst_blocks, int64_t elems_per_block) {
+  REF_PROTECT({
+    auto opts = [](int dev) {
+      auto o = torch::TensorOptions().dtype(torch::kBFloat16);
+      return dev >= 0 ? o.device(torch::kCUDA, dev) : o.device(torch::kCPU);
+    };
+    auto s = torch::from_blob(src, {src_blocks, elems_per_block}, opts(src_dev));
+    auto d = torch::from_blob(dst, {dst_blocks, elems_per_block}, opts(dst_dev));
+    BlockMap m;
+    for (int64_t i = 0; i < num_pairs; ++i) m[pairs[2 * i]] = pairs[2 * i + 1];
+    swap_blocks(s, d, m);
   })
 }
 

@@ -9,7 +9,8 @@ import pytest
 import torch
 
 import aici_b200
-from aici_b200 import _lib, build, tch_cuda, workloads
+from aici_b200 import _lib, build, tch_cuda
+import workloads
 from aici_b200._lib import AiciError
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

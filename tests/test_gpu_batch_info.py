@@ -2,7 +2,8 @@
 import pytest
 import torch
 
-from aici_b200 import _lib, batch_info, tch_cuda, workloads
+from aici_b200 import _lib, batch_info, tch_cuda
+import workloads
 from oracle import batch_info_ref
 from oracle import cpu_oracle as O
 

@@ -1,6 +1,8 @@
 """Multi-GPU parity: KV heads sharded over 2/4/8 GPUs of one box (one process per GPU, NCCL),
-head outputs gathered, result compared on rank 0 with the CPU oracle on the UNSHARDED problem.
-Skipped on a single-GPU box.  Every rank draws the same full tensors and keeps its heads."""
+head outputs gathered, result compared on rank 0 with the CPU oracle on the UNSHARDED problem; the
+fused gather (peer buffers mapped through the C ABI alone) must reproduce the NCCL gather bit for
+bit over consecutive steps.  Skipped on a single-GPU box.  Every rank draws the same full tensors
+and keeps its heads."""
 import os
 import socket
 import traceback
@@ -24,7 +26,8 @@ def _free_port():
 def _worker(rank, world, port, q):
     try:
         import torch.distributed as dist
-        from aici_b200 import _lib, sharding, tch_cuda, workloads
+        from aici_b200 import _lib, sharding, tch_cuda
+        import workloads
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -37,19 +40,43 @@ def _worker(rank, world, port, q):
             shard = sharding.current_shard(kw["num_heads"], kw["num_kv_heads"])
             w = workloads.make_decode(name, dev, shard=shard, **kw)
             tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
+            # three consecutive steps with different queries: NCCL gather as the comparison ...
+            queries = [w.query, (w.query * 2).contiguous(), (w.query * 0.5).contiguous()]
+            fulls = []
+            for qk in queries:
+                out = torch.empty_like(qk)
+                tch_cuda.paged_attention_v1(out, qk, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                            w.block_tables, w.context_lens, 16, w.max_context_len, None)
+                fulls.append(sharding.gather_heads(out).contiguous())
+            # ... and the fused epilogue: rows stored straight into every rank's buffer (mapped through
+            # the library's own peer-memory calls), two buffers used in turn, a reader on the stream
+            # between the steps, the barrier once as a launch of its own and twice folded into the call
+            pg = sharding.PeerGather(w.query.shape[0], kw["num_heads"], 128, dev)
+            pg.barrier()
+            snaps = []
+            for step, qk in enumerate(queries):
+                fold = step > 0
+                tch_cuda.paged_attention_v1_peers(pg.ptrs, kw["num_heads"], pg.head0, qk, w.key_cache,
+                                                  w.value_cache, w.num_kv_heads, w.scale, w.block_tables,
+                                                  w.context_lens, 16, w.max_context_len,
+                                                  barrier_flags=pg.flag_ptrs if fold else None, rank=pg.rank)
+                if not fold:
+                    pg.barrier()
+                snaps.append(pg.tensor.clone())  # the reader
+                pg.flip()
+            torch.cuda.synchronize()
+            for step, (snap, full) in enumerate(zip(snaps, fulls)):
+                assert torch.equal(snap.view(torch.int16), full.view(torch.int16)), "%s fused gather, step %d" % (name, step)
+            # the gather as a call of its own
             out = torch.empty_like(w.query)
             tch_cuda.paged_attention_v1(out, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
                                         w.block_tables, w.context_lens, 16, w.max_context_len, None)
-            full = sharding.gather_heads(out)
-            # the same through the fused epilogue: rows stored straight into every rank's buffer
-            pg = sharding.PeerGather(w.query.shape[0], kw["num_heads"], 128, dev)
-            pg.barrier()
-            tch_cuda.paged_attention_v1_peers(pg.ptrs, kw["num_heads"], pg.head0, w.query, w.key_cache,
-                                              w.value_cache, w.num_kv_heads, w.scale, w.block_tables,
-                                              w.context_lens, 16, w.max_context_len)
+            tch_cuda.gather_heads(pg.ptrs, kw["num_heads"], pg.head0, out)
             pg.barrier()
             torch.cuda.synchronize()
-            assert torch.equal(pg.tensor.view(torch.int16), full.contiguous().view(torch.int16)), name + " fused gather"
+            assert torch.equal(pg.tensor.view(torch.int16), fulls[0].view(torch.int16)), name + " gather_heads"
+            pg.close()
+            full = fulls[0]
             if rank == 0:
                 from oracle import cpu_oracle as O
                 f = workloads.make_decode(name, dev, **kw)  # unsharded, same seed
@@ -67,11 +94,14 @@ def _worker(rank, world, port, q):
             full = sharding.gather_heads(o)
             pg = sharding.PeerGather(w.q.shape[0], kw["num_heads"], 128, dev)
             pg.barrier()
-            tch_cuda.flash_attn_varlen_peers(pg.ptrs, kw["num_heads"], pg.head0, w.q, w.k, w.v, w.cu_seqlens_q,
-                                             w.cu_seqlens_k, w.max_seqlen_q, w.max_seqlen_k, w.scale, True)
-            pg.barrier()
-            torch.cuda.synchronize()
-            assert torch.equal(pg.tensor.view(torch.int16), full.contiguous().view(torch.int16)), name + " fused gather"
+            for _ in range(2):  # both buffers
+                tch_cuda.flash_attn_varlen_peers(pg.ptrs, kw["num_heads"], pg.head0, w.q, w.k, w.v, w.cu_seqlens_q,
+                                                 w.cu_seqlens_k, w.max_seqlen_q, w.max_seqlen_k, w.scale, True)
+                pg.barrier()
+                torch.cuda.synchronize()
+                assert torch.equal(pg.tensor.view(torch.int16), full.contiguous().view(torch.int16)), name + " fused gather"
+                pg.flip()
+            pg.close()
             if rank == 0:
                 from oracle import cpu_oracle as O
                 f = workloads.make_prefill(name, dev, **kw)

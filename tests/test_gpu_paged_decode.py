@@ -4,7 +4,8 @@ definition): max-abs <= 2e-2 and mean-abs <= 2e-3 for bf16 outputs."""
 import pytest
 import torch
 
-from aici_b200 import _lib, tch_cuda, workloads
+from aici_b200 import _lib, tch_cuda
+import workloads
 from oracle import cpu_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -107,33 +108,34 @@ def test_span_traversal_shapes(cuda_device, hq, hkv, ctx):
 
 
 def test_span_and_chunk_traversals_agree(cuda_device):
-    """Same batch through both traversals (the tuning hook selects the fixed-chunk one)."""
+    """Same batch through both traversals (the chunked one through its own entry point)."""
     w = workloads.make_decode("t", cuda_device, num_seqs=48, num_heads=32, num_kv_heads=8,
                               ctx_kind="loguniform", ctx_lo=16, ctx_hi=4000, pool_blocks=8192, seed=365)
     a, b = torch.empty_like(w.query), torch.empty_like(w.query)
     tch_cuda.paged_attention_v1(a, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
                                 w.block_tables, w.context_lens, 16, w.max_context_len, None)
-    _lib.check("tune", _lib.lib().aici_tune_decode_chunk(256))
-    try:
-        tch_cuda.paged_attention_v1(b, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
-                                    w.block_tables, w.context_lens, 16, w.max_context_len, None)
-    finally:
-        _lib.check("tune", _lib.lib().aici_tune_decode_chunk(0))
+    need = _lib.lib().aici_paged_attention_workspace_bytes(48, 32, 8, w.max_context_len)
+    tch_cuda.paged_attention_v1_chunked(b, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
+                                        w.block_tables, w.context_lens, 16, w.max_context_len, 256)
+    # the other traversal changed nothing process-wide: the default call still wants the same scratch
+    assert _lib.lib().aici_paged_attention_workspace_bytes(48, 32, 8, w.max_context_len) == need
     d = (a.float() - b.float()).abs()
     assert float(d.max()) <= 4e-3, float(d.max())  # same tiles, different split points
     assert _lib.last_status() == 0
 
 
-@pytest.mark.parametrize("chunk", [16, 64, 512])
+@pytest.mark.parametrize("chunk", [0, 16, 64, 512])
 def test_chunk_sizes(cuda_device, chunk):
     ctx = [700, 16, 1, 2049, 130]
     q, kc, vc, bt, cl = _case(320, 8, 2, ctx, 300)
-    _lib.check("tune", _lib.lib().aici_tune_decode_chunk(chunk))
-    try:
-        got = _run_v1(cuda_device, q, kc, vc, 2, 0.088, bt, cl)
-    finally:
-        _lib.check("tune", _lib.lib().aici_tune_decode_chunk(0))
-    _check(got, O.paged_attention_v1(q, kc, vc, 2, 0.088, bt, cl))
+    dev = cuda_device
+    out = torch.full(q.shape, float("nan"), dtype=torch.bfloat16, device=dev)
+    tch_cuda.paged_attention_v1_chunked(out, q.to(dev), kc.to(dev), vc.to(dev), 2, 0.088, bt.to(dev),
+                                        cl.to(dev), 16, int(cl.max()), chunk)
+    _check(out.cpu(), O.paged_attention_v1(q, kc, vc, 2, 0.088, bt, cl))
+    with pytest.raises(_lib.AiciError, match="multiple of 16"):
+        tch_cuda.paged_attention_v1_chunked(out, q.to(dev), kc.to(dev), vc.to(dev), 2, 0.088, bt.to(dev),
+                                            cl.to(dev), 16, int(cl.max()), 24)
 
 
 def test_v2_entry_point_and_its_temporaries(cuda_device):

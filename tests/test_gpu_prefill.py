@@ -3,7 +3,8 @@ the CPU oracle's fp32-softmax result.  Tolerance: max-abs <= 2e-2, mean-abs <= 2
 import pytest
 import torch
 
-from aici_b200 import _lib, tch_cuda, workloads
+from aici_b200 import _lib, tch_cuda
+import workloads
 from oracle import cpu_oracle as O
 
 pytestmark = pytest.mark.gpu

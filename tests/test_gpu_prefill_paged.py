@@ -5,7 +5,8 @@ against this repository's packed-K/V kernel.  Tolerance: max-abs 2e-2, mean-abs 
 import pytest
 import torch
 
-from aici_b200 import _lib, tch_cuda, workloads
+from aici_b200 import _lib, tch_cuda
+import workloads
 from oracle import cpu_oracle as O
 
 pytestmark = pytest.mark.gpu

@@ -1,5 +1,10 @@
 """GPU parity tests (bit-exact) for swap_blocks through the C ABI: device <-> page-locked host
-(kernel over PCIe), device <-> pageable host (copy engine), device <-> device."""
+(kernel over PCIe), device <-> pageable host (copy engine), device <-> device -- against the CPU
+oracle and against the reference's own swap_blocks (kernels/vllm/cache_kernels.cu:12-50) run on the
+same inputs through the comparator library."""
+import ctypes
+import os
+
 import pytest
 import torch
 
@@ -8,6 +13,8 @@ from aici_b200._lib import AiciError
 from oracle import cpu_oracle as O
 
 pytestmark = pytest.mark.gpu
+REF_LIB = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref",
+                       "libref_vllm.so")
 
 
 def _cache(nblk, hkv, seed, value=False):
@@ -96,3 +103,62 @@ def test_empty_mapping_and_errors(cuda_device):
     with pytest.raises(AiciError, match="same block shape"):
         tch_cuda.swap_blocks(gpu, _cache(8, 2, 2), {0: 1})
     assert _lib.last_status() == 0
+
+
+def _ref_swap(ref, src, dst, mapping):
+    pairs = torch.tensor([x for s_, d_ in mapping.items() for x in (s_, d_)], dtype=torch.int64)
+    dev = lambda t: t.device.index if t.is_cuda else -1
+    res = ref.ref_swap_blocks(ctypes.c_void_p(src.data_ptr()), dev(src), ctypes.c_void_p(dst.data_ptr()), dev(dst),
+                              ctypes.c_void_p(pairs.data_ptr()), ctypes.c_int64(len(mapping)),
+                              ctypes.c_int64(src.shape[0]), ctypes.c_int64(dst.shape[0]),
+                              ctypes.c_int64(src[0].numel()))
+    assert not res, ctypes.string_at(res)
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("direction", ["device_to_pinned", "pinned_to_device", "device_to_pageable",
+                                       "pageable_to_device", "device_to_device"])
+@pytest.mark.parametrize("hkv,pairs,value", [(8, 37, True), (32, 150, False)])
+def test_bit_exact_vs_reference_swap_blocks(cuda_device, direction, hkv, pairs, value):
+    """Ours and the reference's own function on identical inputs: destinations must agree bit for bit
+    (every block, the untouched ones included) and sources must stay as they were."""
+    if not os.path.exists(REF_LIB):
+        pytest.skip("reference comparator not built (python oracle/build_ref.py)")
+    ref = ctypes.CDLL(REF_LIB)
+    if not hasattr(ref, "ref_swap_blocks"):
+        pytest.skip("comparator library predates ref_swap_blocks: rebuild it (python oracle/build_ref.py --force)")
+    ref.ref_swap_blocks.restype = ctypes.c_void_p
+    n_src, n_dst = 200, 260
+    src0, dst0 = _cache(n_src, hkv, 11, value), _cache(n_dst, hkv, 12, value)
+    src_kind, dst_kind = direction.split("_to_")
+
+    def place(t, kind):
+        if kind == "device":
+            return t.to(cuda_device)
+        return t.clone().pin_memory() if kind == "pinned" else t.clone()
+    m = _mapping(n_src, n_dst, pairs, 13)
+    src_a, dst_a = place(src0, src_kind), place(dst0, dst_kind)
+    src_b, dst_b = place(src0, src_kind), place(dst0, dst_kind)
+    tch_cuda.swap_blocks(src_a, dst_a, m)
+    torch.cuda.synchronize()
+    _ref_swap(ref, src_b, dst_b, m)
+    assert _same(dst_a, dst_b)
+    assert _same(src_a, src0) and _same(src_b, src0)
+    assert not _same(dst_a, dst0)
+    assert _lib.last_status() == 0
+
+
+def test_cache_on_another_gpu_than_the_current_one_is_refused():
+    """The copy kernel runs on the current device, so a cache that lives elsewhere is an error
+    (through the raw C ABI: the Python mirror would make the cache's GPU current itself)."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    torch.cuda.set_device(0)
+    gpu1 = _cache(8, 1, 1).to("cuda:1")
+    host = _cache(8, 1, 2).pin_memory()
+    pairs = torch.tensor([0, 1], dtype=torch.int64)
+    res = _lib.lib().aici_swap_blocks(ctypes.c_void_p(gpu1.data_ptr()), ctypes.c_void_p(host.data_ptr()),
+                                      ctypes.c_void_p(pairs.data_ptr()), 1, ctypes.c_int64(gpu1[0].numel() * 2),
+                                      ctypes.c_int64(8), ctypes.c_int64(8), None)
+    with pytest.raises(AiciError, match="current device"):
+        _lib.check("swap_blocks", res)

@@ -12,7 +12,8 @@ import os
 import pytest
 import torch
 
-from aici_b200 import _lib, tch_cuda, workloads
+from aici_b200 import _lib, tch_cuda
+import workloads
 from oracle import cpu_oracle as O
 
 pytestmark = pytest.mark.gpu

@@ -1,7 +1,8 @@
 """World-size-2 CPU tests (gloo) of the KV-head sharding and the head-output gather: each rank
 computes its own heads (with the CPU oracle standing in for the kernels) and the gathered result
 must equal the unsharded one.  Also the host-side failure paths: bad divisibility, and a rank
-that never joins the collective (short process-group timeout)."""
+that never joins the collective (short process-group timeout) -- for the gather itself and for the
+exchange of peer-memory handles that sets up the fused gather."""
 import datetime
 import os
 import socket
@@ -12,7 +13,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from aici_b200 import sharding, workloads
+from aici_b200 import sharding
+import workloads
 from oracle import cpu_oracle as O
 
 
@@ -92,6 +94,40 @@ def _worker_missing_rank(rank, world, port, q):
         os._exit(0)
 
 
+def _worker_handle_exchange(rank, world, port, q):
+    try:
+        _init(rank, world, port)
+        got = sharding.exchange_bytes(bytes([rank + 1]) * 64)
+        assert got == [bytes([1]) * 64, bytes([2]) * 64], got
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception:
+        q.put((rank, traceback.format_exc()))
+
+
+def _worker_handle_exchange_missing_rank(rank, world, port, q):
+    try:
+        _init(rank, world, port, timeout_s=5)
+        if rank == 1:
+            # dies on the host before it published its handle
+            q.put((rank, "left"))
+            q.close()
+            q.join_thread()
+            os._exit(0)
+        try:
+            sharding.exchange_bytes(b"\x07" * 64)
+            q.put((rank, "exchange returned although a rank was missing"))
+        except sharding.ShardingError as e:
+            q.put((rank, "error:" + str(e)[:60]))
+    except Exception:
+        q.put((rank, traceback.format_exc()))
+    finally:
+        q.close()
+        q.join_thread()
+        os._exit(0)
+
+
 def _run(worker, world=2):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -121,13 +157,27 @@ def test_missing_rank_is_an_error_not_a_hang():
     assert res[0].startswith("error:"), res
 
 
+@pytest.mark.timeout(300)
+def test_handle_exchange_world2():
+    res = _run(_worker_handle_exchange)
+    assert res == {0: "ok", 1: "ok"}, res
+
+
+@pytest.mark.timeout(300)
+def test_handle_exchange_with_a_missing_rank_is_an_error_string_not_a_hang():
+    res = _run(_worker_handle_exchange_missing_rank)
+    assert res[1] == "left"
+    assert res[0].startswith("error:handle exchange failed"), res
+
+
 def test_check_world_rejects_bad_divisibility():
     sharding.check_world(32, 8, 8)
     with pytest.raises(sharding.ShardingError, match="divisible"):
         sharding.check_world(32, 8, 3)
     with pytest.raises(sharding.ShardingError):
-        workloads_shard = workloads.Shard(0, 3)
-        sharding.shard_heads(torch.zeros(2, 8, 4), workloads_shard)
+        sharding.shard_heads(torch.zeros(2, 8, 4), sharding.Shard(0, 3))
+    with pytest.raises(sharding.ShardingError, match="initialised process group"):
+        sharding.exchange_bytes(b"x")
     assert sharding.current_shard(8, 4).world == 1
     x = torch.randn(3, 4, 8)
     assert torch.equal(sharding.gather_heads(x), x)

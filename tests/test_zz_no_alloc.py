@@ -13,7 +13,8 @@ import ctypes
 import pytest
 import torch
 
-from aici_b200 import _lib, tch_cuda, workloads
+from aici_b200 import _lib, tch_cuda
+import workloads
 
 pytestmark = pytest.mark.gpu
 MAX_ABS, MEAN_ABS = 2e-2, 2e-3

@@ -1,4 +1,5 @@
-"""Seeded synthetic inputs for the five attention-path configurations.
+"""Seeded synthetic inputs for the five attention-path configurations (benchmark and test harness;
+not part of the product package).
 
 The reference publishes no dataset for this path; these generators ARE the inputs: shapes,
 context-length distributions and block-table construction follow the configuration list the
@@ -16,6 +17,8 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
 import torch
+
+from aici_b200.sharding import Shard
 
 HEAD_DIM = 128
 BLOCK_SIZE = 16
@@ -38,23 +41,6 @@ def randn_bf16(shape, device, gen: torch.Generator, chunk: int = 1 << 26) -> tor
         m = min(chunk, n - i)
         out[i:i + m] = torch.randn(m, dtype=torch.float32, device=device, generator=gen).to(torch.bfloat16)
     return out.view(*shape)
-
-
-@dataclass
-class Shard:
-    """KV-head sharding: rank r of `world` owns kv heads [r*Hkv/world, (r+1)*Hkv/world) and the
-    matching query heads (the reference's get_num_heads_parallel, rllm-cuda/src/llm/config.rs:49-51)."""
-    rank: int = 0
-    world: int = 1
-
-    def kv_slice(self, num_kv_heads: int) -> slice:
-        assert num_kv_heads % self.world == 0, "num_kv_heads must divide by the world size"
-        n = num_kv_heads // self.world
-        return slice(self.rank * n, (self.rank + 1) * n)
-
-    def q_slice(self, num_heads: int) -> slice:
-        n = num_heads // self.world
-        return slice(self.rank * n, (self.rank + 1) * n)
 
 
 @dataclass
