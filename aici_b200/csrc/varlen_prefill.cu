@@ -32,9 +32,25 @@ constexpr int kBN = 128;               // keys per tile
 constexpr int kHD = 128;               // head size
 constexpr int kPanelBytes = 128 * 128; // [128 rows][64 bf16] = one 128B-swizzled panel
 constexpr int kTileBytes = 2 * kPanelBytes;
-constexpr int kKvStages = 4;           // ring of K/V tiles (K_j and V_j alternate)
-constexpr int kPrefillThreads = 320;   // 8 softmax warps + producer + MMA issuer
-constexpr uint32_t kTmemCols = 512;    // S0/P0 [0,128) S1/P1 [128,256) O0 [256,384) O1 [384,512)
+constexpr int kMaxKvStages = 4;        // ring of K/V tiles (K_j and V_j alternate)
+
+// Two shapes of the same kernel.  kTiles = 2 (long sequences): one CTA per SM owns two query tiles
+// that share their K/V tiles; all 512 TMEM columns (S0/P0 [0,128) S1/P1 [128,256) O0 [256,384)
+// O1 [384,512)), a 4-stage K/V ring, 8 softmax warps.  kTiles = 1 (short sequences): one query tile,
+// 256 TMEM columns (S/P [0,128) O [128,256)), a 2-stage ring, 4 softmax warps -- half the shared
+// memory and half the tensor memory, so TWO CTAs share an SM and one CTA's fill (barriers, TMEM
+// allocation, first loads) and drain (epilogue, stores, exit) run under the other's MMAs.
+template <int kTiles>
+struct PrefillCfg {
+  static constexpr int kStages = kTiles == 2 ? 4 : 2;
+  static constexpr int kSoftmaxWarps = 4 * kTiles;
+  static constexpr int kProducerWarp = 4 * kTiles;
+  static constexpr int kMmaWarp = 4 * kTiles + 1;
+  static constexpr int kThreads = (4 * kTiles + 2) * 32;
+  static constexpr uint32_t kCols = 256u * kTiles;
+  static constexpr int kSmemBytes = (kTiles + kStages) * kTileBytes + 1024 /*align*/ + 256 /*PrefillSmem*/;
+  static constexpr int kCtasPerSm = kTiles == 2 ? 1 : 2;
+};
 constexpr float kRescaleThreshold = 8.f;  // log2 units: the running reference moves once a score exceeds it by this
 constexpr float kRescaleSum = 256.f;      // single-pass tiles: a row sum above this moves the reference (some score is 2^8 above it, or many are above it)
 constexpr float kDangerSum = 1e30f;       // single-pass tiles: a row sum at or above this (or NaN) means the tile is redone exactly
@@ -67,7 +83,7 @@ struct OutMaps {
 };
 
 struct PrefillSmem {
-  uint64_t q_full[2], kv_full[kKvStages], kv_empty[kKvStages], s_full[2], p_ready[2], o_full[2], staged[2], drain;
+  uint64_t q_full[2], kv_full[kMaxKvStages], kv_empty[kMaxKvStages], s_full[2], p_ready[2], o_full[2], staged[2], drain;
   uint32_t tmem_base;
   uint32_t aborted;
 };
@@ -78,8 +94,6 @@ struct TileInfo {
   int rows;     // valid rows (<= 128); 0 = this tile does not exist
   int n_tiles;  // key/value tiles it visits; 0 = nothing visible
 };
-
-constexpr int kPrefillSmemBytes = (2 + kKvStages) * kTileBytes + 1024 /*align*/ + 256 /*PrefillSmem*/;
 
 __device__ __forceinline__ void zero_rows(const PrefillParams &p, int q0, const TileInfo &T, int tid,
                                           int nthreads) {
@@ -98,12 +112,17 @@ __device__ __forceinline__ void zero_rows(const PrefillParams &p, int q0, const 
 //   2 KB between 8-token groups); a value tile is 8 blocks of [128 d][16 tokens] loaded with the
 //   32-byte swizzle, one K = 16 MMA per block.  Value columns past the sequence end are zeroed in
 //   shared memory before P V (cache slots there may hold anything, NaN included).
-template <bool kPaged>
-__global__ void __launch_bounds__(kPrefillThreads, 1)
+template <bool kPaged, int kTiles>
+__global__ void __launch_bounds__(PrefillCfg<kTiles>::kThreads, PrefillCfg<kTiles>::kCtasPerSm)
 varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v,
                       const __grid_constant__ OutMaps tmap_o, const PrefillParams p) {
+  using Cfg = PrefillCfg<kTiles>;
+  constexpr int kKvStages = Cfg::kStages;
+  constexpr int kPrefillThreads = Cfg::kThreads;
+  constexpr uint32_t kTmemCols = Cfg::kCols;
+  constexpr uint32_t kOCol = 128u * kTiles;  // first column of O0
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.z;
@@ -126,7 +145,11 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   TileInfo tiles[2];
   {
     int mb[2], hh[2];
-    if (p.pair_heads) {
+    if (kTiles == 1) {
+      mb[0] = n_mblocks - 1 - (int)blockIdx.x;
+      mb[1] = -1;  // no second tile
+      hh[0] = hh[1] = (int)blockIdx.y;
+    } else if (p.pair_heads) {
       mb[0] = mb[1] = n_mblocks - 1 - (int)blockIdx.x;
       hh[0] = 2 * (int)blockIdx.y;
       hh[1] = hh[0] + 1;
@@ -157,8 +180,8 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t *sQ = smem;                       // two tiles
-  uint8_t *sKV = smem + 2 * kTileBytes;     // kKvStages tiles
-  PrefillSmem *sh = reinterpret_cast<PrefillSmem *>(smem + (2 + kKvStages) * kTileBytes);
+  uint8_t *sKV = smem + kTiles * kTileBytes;     // kKvStages tiles
+  PrefillSmem *sh = reinterpret_cast<PrefillSmem *>(smem + (kTiles + kKvStages) * kTileBytes);
 
   if (tid == 0) {
 #pragma unroll
@@ -178,7 +201,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     sh->aborted = 0;
     fence_mbar_init();
   }
-  if (warp == 9) {
+  if (warp == Cfg::kMmaWarp) {
     tmem_alloc(&sh->tmem_base, kTmemCols);
     tmem_relinquish();
   }
@@ -187,7 +210,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
 
-  if (warp == 8) {
+  if (warp == Cfg::kProducerWarp) {
     // ---------------------------------------------------------------- TMA producer -----------
     if (lane == 0) {
       tma_prefetch_desc(&tmap_q);
@@ -254,7 +277,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tma_load_3d(dst + kPanelBytes, tm, 64, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == Cfg::kMmaWarp) {
     // ---------------------------------------------------------------- MMA issuer -------------
     constexpr uint32_t idesc_s = idesc_bf16(kBM, kBN, false);
     constexpr uint32_t idesc_pv = idesc_bf16(kBM, kHD, !kPaged);  // packed V: MN-major; cache V: K-major
@@ -293,7 +316,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const uint32_t vstep = kPaged ? 4096u : 2048u;
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks)
-          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + 8 * ks, vdesc + (uint64_t)((ks * vstep) >> 4),
+          umma_ts(tmem_base + kOCol + t * 128, tmem_base + t * 128 + 8 * ks, vdesc + (uint64_t)((ks * vstep) >> 4),
                   idesc_pv, (!first || ks > 0) ? 1u : 0u);
         if (last) tc_commit(&sh->o_full[t]);
       }
@@ -380,7 +403,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     int lim_row = lk;
     if (p.causal) lim_row = min(lk, qr + 1 + lk - lq);
     const uint32_t t_s = tmem_base + t * 128 + ((uint32_t)(quad * 32) << 16);
-    const uint32_t t_o = tmem_base + 256 + t * 128 + ((uint32_t)(quad * 32) << 16);
+    const uint32_t t_o = tmem_base + kOCol + t * 128 + ((uint32_t)(quad * 32) << 16);
     const float sc = p.scale_log2e;
     float m_used = -INFINITY, m_next = -INFINITY, l_sum = 0.f;
     bool ok = true, pending = false;
@@ -649,7 +672,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   // ---- teardown ------------------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == Cfg::kMmaWarp) {
     if (sh->aborted) {
       // bounded wait for whatever the tensor pipe still owes before the columns are released
       if (lane == 0) tc_commit(&sh->drain);
@@ -765,25 +788,49 @@ static char *make_cache_tmap(const char *fn, CUtensorMap *map, const void *base,
   return nullptr;
 }
 
-template <bool kPaged>
-static char *launch_prefill(const char *fn, const CUtensorMap &tq, const CUtensorMap &tk,
-                            const CUtensorMap &tv, const OutMaps &to, PrefillParams &p, int num_heads,
-                            int batch, int max_seqlen_q, cudaStream_t stream) {
+// Sequences up to this many keys take the one-tile shape (two CTAs per SM), longer ones the
+// two-tile shape: with few key tiles per query tile a CTA's fixed cost (fill and drain, about as long
+// as three key tiles) is what two resident CTAs hide; with many, sharing each K/V tile between two
+// query tiles (half the shared-memory traffic) is worth more.
+#ifndef AICI_PREFILL_ONE_TILE_MAX_K
+#define AICI_PREFILL_ONE_TILE_MAX_K 1024
+#endif
+
+template <bool kPaged, int kTiles>
+static char *launch_prefill_shape(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
+                                  const OutMaps &to, PrefillParams &p, int num_heads, int batch,
+                                  int max_seqlen_q, cudaStream_t stream) {
+  using Cfg = PrefillCfg<kTiles>;
   static OncePerDevice once;
   if (char *e = once.run([]() -> char * {
-        AICI_CUDA(cudaFuncSetAttribute(varlen_prefill_kernel<kPaged>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmemBytes));
+        AICI_CUDA(cudaFuncSetAttribute(varlen_prefill_kernel<kPaged, kTiles>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         return nullptr;
       }))
     return e;
-  // two tiles per CTA: two heads of one kv group when the group is even, else two row tiles
-  p.pair_heads = (p.group % 2 == 0) ? 1 : 0;
   const int mblocks = (max_seqlen_q + kBM - 1) / kBM;
-  dim3 grid(p.pair_heads ? mblocks : (mblocks + 1) / 2, p.pair_heads ? num_heads / 2 : num_heads, batch);
-  varlen_prefill_kernel<kPaged><<<grid, kPrefillThreads, kPrefillSmemBytes, stream>>>(tq, tk, tv, to, p);
+  dim3 grid;
+  if (kTiles == 1) {
+    grid = dim3(mblocks, num_heads, batch);
+  } else {
+    // two tiles per CTA: two heads of one kv group when the group is even, else two row tiles
+    p.pair_heads = (p.group % 2 == 0) ? 1 : 0;
+    grid = dim3(p.pair_heads ? mblocks : (mblocks + 1) / 2, p.pair_heads ? num_heads / 2 : num_heads, batch);
+  }
+  varlen_prefill_kernel<kPaged, kTiles><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, to, p);
   AICI_CUDA(cudaGetLastError());
-  (void)fn;
   return nullptr;
+}
+
+template <bool kPaged>
+static char *launch_prefill(const char *fn, const CUtensorMap &tq, const CUtensorMap &tk,
+                            const CUtensorMap &tv, const OutMaps &to, PrefillParams &p, int num_heads,
+                            int batch, int max_seqlen_q, int max_seqlen_k, cudaStream_t stream) {
+  (void)fn;
+  p.pair_heads = 0;
+  if (max_seqlen_k <= AICI_PREFILL_ONE_TILE_MAX_K)
+    return launch_prefill_shape<kPaged, 1>(tq, tk, tv, to, p, num_heads, batch, max_seqlen_q, stream);
+  return launch_prefill_shape<kPaged, 2>(tq, tk, tv, to, p, num_heads, batch, max_seqlen_q, stream);
 }
 
 }  // namespace aici
@@ -864,7 +911,7 @@ static char *mha_varlen_fwd_impl(const char *fn, void *const *outs, int world, i
   for (int w = 0; w < world; ++w)  // the kernel reads m[w] for w < world only
     if (char *e = make_tmap(fn, &to.m[w], outs[w], total_q, out_head0 + num_heads, o_tok_stride, o_head_stride))
       return e;
-  return launch_prefill<false>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q,
+  return launch_prefill<false>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q, max_seqlen_k,
                                static_cast<cudaStream_t>(stream));
 }
 
@@ -971,11 +1018,10 @@ extern "C" char *aici_mha_varlen_paged_fwd(void *out, const void *q, const void 
   p.k_lens = context_lens;
   p.max_blocks = max_num_blocks_per_seq;
   p.num_blocks = num_blocks;
-  (void)max_context_len;
   OutMaps to = {};
   p.total_q = total_q;
   p.tma_store = 1;
   if (char *e = make_tmap(fn, &to.m[0], out, total_q, num_heads, o_tok_stride, o_head_stride)) return e;
-  return launch_prefill<true>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q,
+  return launch_prefill<true>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q, max_context_len,
                               static_cast<cudaStream_t>(stream));
 }

@@ -327,23 +327,35 @@ class Runner:
             fn()
         return g
 
-    def time_flushed(self, fn, iters, warm=3, graph=True):
-        """Median device time (ms) of one launch of fn with the L2 flushed before it; max over ranks.
-        fn is replayed as a CUDA graph, so the figure does not depend on the host's launch speed."""
-        run = self.capture(fn).replay if graph else fn
-        ts = []
-        for i in range(warm + iters):
-            if self.world > 1:
-                self.dist.barrier()
-            self.flush()  # also gives the host time to queue the launch behind it
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            run()
-            b.record()
-            torch.cuda.synchronize()
-            if i >= warm:
-                ts.append(a.elapsed_time(b))
-        return self.max_over_ranks(statistics.median(ts))
+    def time_rotating(self, fns, reps, warm=2):
+        """Device time (ms) of ONE launch: the calls in `fns` -- the same operation on distinct
+        buffer sets whose sizes add up to several times the L2, so that every launch finds its
+        data in HBM -- are captured back to back into one CUDA graph, the graph is replayed `reps`
+        times between two events, and the elapsed time is divided by the number of launches.  Max
+        over ranks.  Timing a run of launches instead of one keeps the cost of recording an event
+        and starting a graph (several microseconds) out of kernels that take ten."""
+        def all_once():
+            for f in fns:
+                f()
+        g = self.capture(all_once)
+        for _ in range(warm):
+            g.replay()
+        self.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            g.replay()
+        b.record()
+        self.barrier()
+        return self.max_over_ranks(a.elapsed_time(b)) / (reps * len(fns))
+
+
+def copies_to_stream(nbytes, at_least=MIN_STREAM_BYTES, cap=32):
+    """How many distinct buffer sets of nbytes a run of launches needs to stream at_least bytes."""
+    n = 1
+    while n * nbytes < at_least and n < cap:
+        n += 1
+    return n
 
 
 def roof(kind, work_local, ms, peaks, extra=None):
@@ -541,55 +553,65 @@ def run_ours(args):
         del full
     torch.cuda.empty_cache()
 
-    # ---- the other configurations: device time per launch, L2 flushed before each -------------
+    # ---- the other configurations: device time per launch over rotating buffer sets ------------
     configs = {}
-    cfg_iters = max(5, min(args.steps, 20))
+    reps = max(5, min(args.steps, 20))
     if not args.headline_only:
         for key, make in (("cfg3", workloads.decode_llama3_8b), ("cfg5_decode", workloads.decode_mixed_step)):
             cw = make(dev, shard=shard)
+            tch_cuda.reshape_and_cache(cw.new_key, cw.new_value, cw.key_cache, cw.value_cache, cw.slot_mapping)
+            n_sets = copies_to_stream(cw.algorithmic_bytes())
+            cpools = [(cw.key_cache, cw.value_cache)] + [(cw.key_cache.clone(), cw.value_cache.clone())
+                                                         for _ in range(n_sets - 1)]
             o_loc = torch.empty_like(cw.query)
             cpg = None
             if fused:
-                cpg = sharding.PeerGather(cw.query.shape[0], cw.num_heads * world, 128, dev, buffers=1)
+                cpg = sharding.PeerGather(cw.query.shape[0], cw.num_heads * world, 128, dev, buffers=2)
                 cpg.barrier()
 
-            def dec(cw=cw, o_loc=o_loc, cpg=cpg):
+            def dec(i, cw=cw, o_loc=o_loc, cpg=cpg, cpools=cpools):
+                kc_, vc_ = cpools[i % len(cpools)]
                 if cpg is not None:
-                    tch_cuda.paged_attention_v1_peers(cpg.ptrs, cw.num_heads * world, cpg.head0, cw.query,
-                                                      cw.key_cache, cw.value_cache, cw.num_kv_heads, cw.scale,
-                                                      cw.block_tables, cw.context_lens, 16, cw.max_context_len,
+                    tch_cuda.paged_attention_v1_peers(cpg._ptrs[i % 2], cw.num_heads * world, cpg.head0, cw.query,
+                                                      kc_, vc_, cw.num_kv_heads, cw.scale, cw.block_tables,
+                                                      cw.context_lens, 16, cw.max_context_len,
                                                       barrier_flags=cpg.flag_ptrs, rank=cpg.rank)
                 else:
-                    tch_cuda.paged_attention_v1(o_loc, cw.query, cw.key_cache, cw.value_cache, cw.num_kv_heads,
-                                                cw.scale, cw.block_tables, cw.context_lens, 16,
-                                                cw.max_context_len, None)
-            tch_cuda.reshape_and_cache(cw.new_key, cw.new_value, cw.key_cache, cw.value_cache, cw.slot_mapping)
-            ms = R.time_flushed(dec, cfg_iters)
+                    tch_cuda.paged_attention_v1(o_loc, cw.query, kc_, vc_, cw.num_kv_heads, cw.scale,
+                                                cw.block_tables, cw.context_lens, 16, cw.max_context_len, None)
+            n_launch = n_sets if n_sets % 2 == 0 or cpg is None else 2 * n_sets
+            ms = R.time_rotating([lambda i=i: dec(i) for i in range(n_launch)], reps)
             configs[key] = roof("hbm", cw.algorithmic_bytes(), ms, peaks,
-                                {"workload": cw.name, "includes": "decode + merge launches" +
+                                {"workload": cw.name, "pool_copies": n_sets,
+                                 "includes": "decode + merge launches" +
                                  (", peer stores and barrier" if cpg is not None else "")})
-            dec()
+            dec(0)
             torch.cuda.synchronize()
-            g_out = (cpg.tensor if cpg is not None else
+            g_out = (cpg.tensors[0] if cpg is not None else
                      (sharding.gather_heads(o_loc) if world > 1 else o_loc)).clone()
             if cpg is not None:
                 cpg.close()
+            del cpools
             if key == "cfg5_decode":
-                # the AICI fork on this pool: 32 sequences x 4 children, last block each, 4 "layers"
+                # the AICI fork on this pool: 32 sequences x 4 children, last block each, 4 "layers";
+                # eight different sets of 32 parents (and of free blocks) are copied in turn
                 rows_ = [cw.block_tables[i, :(c + 15) // 16].tolist() for i, c in enumerate(cw.context_list)]
                 used = set(b for r in rows_ for b in r)
                 free = [b for b in range(cw.key_cache.shape[0]) if b not in used]
-                mapping = workloads.fork_block_mapping(rows_, 32, 4, free)
-                flat = torch.tensor([x for s_, ds in mapping.items() for d_ in ds for x in (s_, d_)],
-                                    dtype=torch.int64)
                 layers = 4
                 kcs = [cw.key_cache] + [cw.key_cache.clone() for _ in range(layers - 1)]
                 vcs = [cw.value_cache] + [cw.value_cache.clone() for _ in range(layers - 1)]
-                ms = R.time_flushed(lambda: tch_cuda.copy_blocks(kcs, vcs, flat), cfg_iters)
+                maps = []
+                for j in range(8):
+                    parents = rows_[(24 * j) % (len(rows_) - 32):][:32]
+                    mapping = workloads.fork_block_mapping(parents, 32, 4, free[128 * j:128 * (j + 1)])
+                    maps.append((mapping, torch.tensor([x for s_, ds in mapping.items() for d_ in ds
+                                                        for x in (s_, d_)], dtype=torch.int64)))
+                ms = R.time_rotating([lambda f=f: tch_cuda.copy_blocks(kcs, vcs, f) for _m, f in maps], reps)
                 blk_bytes = cw.num_kv_heads * 128 * 16 * 2
-                pairs = flat.numel() // 2
+                pairs = maps[0][1].numel() // 2
                 ok = True
-                for s_, ds in mapping.items():
+                for s_, ds in maps[0][0].items():
                     for d_ in ds:
                         for l in range(layers):
                             ok = ok and torch.equal(kcs[l][d_].view(torch.int16), kcs[l][s_].view(torch.int16)) \
@@ -597,7 +619,9 @@ def run_ours(args):
                 configs["cfg5_copy_blocks"] = roof(
                     "hbm", pairs * layers * 2 * blk_bytes * 2, ms, peaks,
                     {"workload": "fork of 32 sequences into 4 children, last block each: %d pairs x %d layers"
-                                 % (pairs, layers), "bit_exact": R.all_true(ok)})
+                                 % (pairs, layers), "bit_exact": R.all_true(ok),
+                     "note": "%.0f MB per launch: the launch ramp weighs as much as the copy" %
+                             (pairs * layers * 2 * blk_bytes * 2 / 1e6)})
                 del kcs, vcs
             del cw.key_cache, cw.value_cache
             torch.cuda.empty_cache()
@@ -609,36 +633,50 @@ def run_ours(args):
 
         # config 5, prefill part (8 chunks of 512) and the cache write of its 4288 tokens
         pw5 = workloads.prefill_mixed_chunks(dev, shard=shard)
-        ms = R.time_flushed(lambda: tch_cuda.flash_attn_varlen(pw5.q, pw5.k, pw5.v, pw5.cu_seqlens_q,
-                                                               pw5.cu_seqlens_k, pw5.max_seqlen_q,
-                                                               pw5.max_seqlen_k, pw5.scale, True), cfg_iters)
+        p5_bytes = (pw5.q.numel() * 2 + pw5.k.numel() * 2) * 2
+        sets5 = [(pw5.q, pw5.k, pw5.v)] + [(pw5.q.clone(), pw5.k.clone(), pw5.v.clone())
+                                           for _ in range(copies_to_stream(p5_bytes, 4 * L2_BYTES) - 1)]
+        ms = R.time_rotating([lambda t=t: tch_cuda.flash_attn_varlen(t[0], t[1], t[2], pw5.cu_seqlens_q,
+                                                                     pw5.cu_seqlens_k, pw5.max_seqlen_q,
+                                                                     pw5.max_seqlen_k, pw5.scale, True)
+                              for t in sets5], reps)
         configs["cfg5_prefill"] = roof("tensor", pw5.flops(), ms, peaks, {"workload": pw5.name})
         o5 = tch_cuda.flash_attn_varlen(pw5.q, pw5.k, pw5.v, pw5.cu_seqlens_q, pw5.cu_seqlens_k,
                                         pw5.max_seqlen_q, pw5.max_seqlen_k, pw5.scale, True)
         g5 = sharding.gather_heads(o5) if world > 1 else o5
         if rank == 0:
             parity["cfg5_prefill"], _ = prefill_parity(workloads.prefill_mixed_chunks(dev), g5, n_rows=256)
+        del sets5
         hkv5 = pw5.k.shape[1]
         n_tok = 4288
         nb5 = n_tok // 16 + 8
-        kc5 = torch.zeros(nb5, hkv5, 16, 16, 8, dtype=torch.bfloat16, device=dev)
-        vc5 = torch.zeros(nb5, hkv5, 128, 16, dtype=torch.bfloat16, device=dev)
+        rc_bytes = n_tok * hkv5 * 128 * 2 * 2 * 2
         kk = torch.cat([pw5.k, pw5.k[:n_tok - pw5.k.shape[0]]]).contiguous()
         vv = torch.cat([pw5.v, pw5.v[:n_tok - pw5.v.shape[0]]]).contiguous()
         slots5 = torch.arange(n_tok, dtype=torch.int32, device=dev)
-        ms = R.time_flushed(lambda: tch_cuda.reshape_and_cache(kk, vv, kc5, vc5, slots5), cfg_iters)
+        rc_sets = []
+        for j in range(copies_to_stream(rc_bytes, 4 * L2_BYTES)):
+            rc_sets.append((kk if j == 0 else kk.clone(), vv if j == 0 else vv.clone(),
+                            torch.zeros(nb5, hkv5, 16, 16, 8, dtype=torch.bfloat16, device=dev),
+                            torch.zeros(nb5, hkv5, 128, 16, dtype=torch.bfloat16, device=dev)))
+        ms = R.time_rotating([lambda t=t: tch_cuda.reshape_and_cache(t[0], t[1], t[2], t[3], slots5)
+                              for t in rc_sets], reps)
         ok = True
         if rank == 0:
             from oracle import cpu_oracle as O
+            kc5, vc5 = rc_sets[-1][2], rc_sets[-1][3]
             kr, vr = torch.zeros_like(kc5).cpu(), torch.zeros_like(vc5).cpu()
             O.reshape_and_cache(kk.cpu(), vv.cpu(), kr, vr, slots5.cpu())
             ok = torch.equal(kc5.cpu().view(torch.int16), kr.view(torch.int16)) and \
                 torch.equal(vc5.cpu().view(torch.int16), vr.view(torch.int16))
         configs["cfg5_reshape_and_cache"] = roof(
-            "hbm", n_tok * hkv5 * 128 * 2 * 2 * 2, ms, peaks,
+            "hbm", rc_bytes, ms, peaks,
             {"workload": "4288 tokens (8 x 512 prefill + 192 decode), block-aligned chunks", "bit_exact": ok})
-        del pw5, kc5, vc5, kk, vv, o5, g5
+        del pw5, rc_sets, kk, vv, o5, g5
         torch.cuda.empty_cache()
+        for v_ in configs.values():
+            v_["timing"] = "one CUDA graph of back-to-back launches over distinct buffer sets (>= 4x L2 in all), " \
+                           "replayed %d times between two events; ms per launch" % reps
 
     # ---- long-context causal prefill (2 x 32768, 64 q / 8 kv heads; heads split over ranks) ---
     pw = workloads.prefill_long(dev, shard=shard)
@@ -1039,6 +1077,30 @@ def run_profile_case(args):
         torch.cuda.synchronize()
         print(json.dumps({"profile_case": "decode", "seqs": w.query.shape[0], "heads": w.num_heads,
                           "algorithmic_bytes": w.algorithmic_bytes()}))
+    elif args.profile == "small_ops":
+        # the short launches of the mixed step, each three times with the L2 flushed before it:
+        # cache write of 4288 tokens, fork copy of 128 pairs x 4 layers, prefill of 8 x 512
+        pw = workloads.prefill_mixed_chunks(dev)
+        flush = torch.empty(4 * L2_BYTES, dtype=torch.uint8, device=dev)
+        n_tok, hkv = 4288, pw.k.shape[1]
+        kk = torch.cat([pw.k, pw.k[:n_tok - pw.k.shape[0]]]).contiguous()
+        kc = torch.zeros(n_tok // 16 + 8, hkv, 16, 16, 8, dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros(n_tok // 16 + 8, hkv, 128, 16, dtype=torch.bfloat16, device=dev)
+        slots = torch.arange(n_tok, dtype=torch.int32, device=dev)
+        pool_k = [torch.zeros(1024, hkv, 16, 16, 8, dtype=torch.bfloat16, device=dev) for _ in range(4)]
+        pool_v = [torch.zeros(1024, hkv, 128, 16, dtype=torch.bfloat16, device=dev) for _ in range(4)]
+        pairs = torch.tensor([x for i in range(128) for x in (i, 512 + i)], dtype=torch.int64)
+        for _ in range(3):
+            flush.zero_()
+            tch_cuda.reshape_and_cache(kk, kk, kc, vc, slots)
+            flush.zero_()
+            tch_cuda.copy_blocks(pool_k, pool_v, pairs)
+            flush.zero_()
+            tch_cuda.flash_attn_varlen(pw.q, pw.k, pw.v, pw.cu_seqlens_q, pw.cu_seqlens_k, pw.max_seqlen_q,
+                                       pw.max_seqlen_k, pw.scale, True)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_case": "small_ops", "reshape_and_cache_bytes": n_tok * hkv * 128 * 8,
+                          "copy_blocks_bytes": 128 * 4 * 2 * hkv * 128 * 16 * 2 * 2, "prefill_flops": pw.flops()}))
     elif args.profile == "prefill_chunks":
         pw = workloads.prefill_mixed_chunks(dev)
         flush = torch.empty(4 * L2_BYTES, dtype=torch.uint8, device=dev)
@@ -1074,7 +1136,7 @@ def main():
                          "(what rLLM's --profile-step does), for captures limited to the profiler API range")
     ap.add_argument("--suite", action="store_true",
                     help="time all five configurations at the current world size and print one JSON object")
-    ap.add_argument("--profile", default=None, choices=["decode", "prefill", "prefill_chunks"],
+    ap.add_argument("--profile", default=None, choices=["decode", "prefill", "prefill_chunks", "small_ops"],
                     help="run a small case three times for a profiler capture and exit")
     ap.add_argument("--profile-world", type=int, default=1,
                     help="with --profile decode: run rank 0's shard of a run on this many GPUs")

@@ -11,9 +11,15 @@ pytestmark = pytest.mark.gpu
 MAX_ABS, MEAN_ABS = 2e-2, 2e-3
 
 
-def _run(dev, w, causal=True):
+# The kernel has two shapes: one query tile per CTA (two CTAs per SM) for sequences of at most 1024
+# keys, two query tiles per CTA above that; max_seqlen_k, an upper bound the caller passes, is what
+# selects.  Passing a loose bound runs a short batch through the long-sequence shape.
+SHAPES = [pytest.param(None, id="shape_by_length"), pytest.param(4096, id="two_tile_shape")]
+
+
+def _run(dev, w, causal=True, max_k=None):
     return tch_cuda.flash_attn_varlen(w.q, w.k, w.v, w.cu_seqlens_q, w.cu_seqlens_k, w.max_seqlen_q,
-                                      w.max_seqlen_k, w.scale, causal)
+                                      max_k or w.max_seqlen_k, w.scale, causal)
 
 
 def _check_full(w, out, causal=True):
@@ -26,9 +32,10 @@ def _check_full(w, out, causal=True):
     return want
 
 
-def test_config1_small_varlen(cuda_device):
+@pytest.mark.parametrize("max_k", SHAPES)
+def test_config1_small_varlen(cuda_device, max_k):
     w = workloads.prefill_small(cuda_device)
-    out = _run(cuda_device, w)
+    out = _run(cuda_device, w, max_k=max_k)
     _check_full(w, out)
     assert _lib.last_status() == 0
 
@@ -39,10 +46,11 @@ def test_config1_small_varlen(cuda_device):
     ([200, 40], [72, 8], 4, 1),                                 # k_len < q_len: leading rows see nothing
     ([512] * 3, [1536] * 3, 8, 2),                              # config-5 variant with 1024 cached tokens
 ])
-def test_ragged_and_bottom_right_mask(cuda_device, lens_q, lens_k, hq, hkv):
+@pytest.mark.parametrize("max_k", SHAPES)
+def test_ragged_and_bottom_right_mask(cuda_device, lens_q, lens_k, hq, hkv, max_k):
     w = workloads.make_prefill("t", cuda_device, lens_q=lens_q, lens_k=lens_k, num_heads=hq,
                                num_kv_heads=hkv, seed=77)
-    out = _run(cuda_device, w)
+    out = _run(cuda_device, w, max_k=max_k)
     want = _check_full(w, out)
     if lens_k[0] < lens_q[0]:
         assert float(out[:lens_q[0] - lens_k[0]].float().abs().max()) == 0.0
@@ -50,10 +58,11 @@ def test_ragged_and_bottom_right_mask(cuda_device, lens_q, lens_k, hq, hkv):
     assert _lib.last_status() == 0
 
 
-def test_non_causal(cuda_device):
+@pytest.mark.parametrize("max_k", SHAPES)
+def test_non_causal(cuda_device, max_k):
     w = workloads.make_prefill("t", cuda_device, lens_q=[100, 260], lens_k=[150, 260], num_heads=4,
                                num_kv_heads=2, seed=78)
-    _check_full(w, _run(cuda_device, w, causal=False), causal=False)
+    _check_full(w, _run(cuda_device, w, causal=False, max_k=max_k), causal=False)
 
 
 def test_strided_inputs_from_fused_qkv(cuda_device):
@@ -70,7 +79,8 @@ def test_strided_inputs_from_fused_qkv(cuda_device):
     assert mx <= MAX_ABS and mean <= MEAN_ABS, (mx, mean)
 
 
-def test_large_scores_exercise_the_lazy_rescale(cuda_device):
+@pytest.mark.parametrize("max_k", SHAPES)
+def test_large_scores_exercise_the_lazy_rescale(cuda_device, max_k):
     """Scores that keep growing along the key axis force the running maximum to move by more
     than the rescale threshold many times."""
     n, hq = 1024, 2
@@ -81,13 +91,14 @@ def test_large_scores_exercise_the_lazy_rescale(cuda_device):
     ramp = torch.linspace(0.2, 3.0, n, device=cuda_device).view(n, 1, 1)
     k = (k * ramp).to(torch.bfloat16)
     cu = torch.tensor([0, n], dtype=torch.int32, device=cuda_device)
-    out = tch_cuda.flash_attn_varlen(q, k, v, cu, cu, n, n, 0.5, True)
+    out = tch_cuda.flash_attn_varlen(q, k, v, cu, cu, n, max_k or n, 0.5, True)
     want = O.flash_attn_varlen(q.cpu(), k.cpu(), v.cpu(), cu.cpu(), cu.cpu(), n, n, 0.5, True)
     mx, mean = O.error_stats(out.cpu(), want)
     assert mx <= 4e-2 and mean <= MEAN_ABS, (mx, mean)  # peaked softmax: |out| up to ~4, bf16 ulp 1.6e-2
 
 
-def test_score_jump_beyond_the_single_pass_range(cuda_device):
+@pytest.mark.parametrize("max_k", SHAPES)
+def test_score_jump_beyond_the_single_pass_range(cuda_device, max_k):
     """Keys of the last tiles are 8x larger: scores jump by far more than the range the single-pass
     softmax may absorb, so those tiles must be redone against their exact maximum (no inf/NaN)."""
     n, hq = 640, 2
@@ -98,7 +109,7 @@ def test_score_jump_beyond_the_single_pass_range(cuda_device):
     k[384:] = (k[384:].float() * 8).to(torch.bfloat16)
     k[600:] = (k[600:].float() * 4).to(torch.bfloat16)
     cu = torch.tensor([0, n], dtype=torch.int32, device=cuda_device)
-    out = tch_cuda.flash_attn_varlen(q, k, v, cu, cu, n, n, 1.0, True)
+    out = tch_cuda.flash_attn_varlen(q, k, v, cu, cu, n, max_k or n, 1.0, True)
     want = O.flash_attn_varlen(q.cpu(), k.cpu(), v.cpu(), cu.cpu(), cu.cpu(), n, n, 1.0, True)
     got = out.cpu().float()
     assert torch.isfinite(got).all()
@@ -106,9 +117,10 @@ def test_score_jump_beyond_the_single_pass_range(cuda_device):
     assert mx <= 4e-2 and mean <= MEAN_ABS, (mx, mean)  # one-hot softmax rows: |out| up to ~4
 
 
-def test_mixed_step_prefill_chunks(cuda_device):
+@pytest.mark.parametrize("max_k", SHAPES)
+def test_mixed_step_prefill_chunks(cuda_device, max_k):
     w = workloads.prefill_mixed_chunks(cuda_device)
-    _check_full(w, _run(cuda_device, w))
+    _check_full(w, _run(cuda_device, w, max_k=max_k))
 
 
 def test_long_context_sampled_rows(cuda_device):
@@ -161,7 +173,8 @@ def test_config4_full_size_sampled_rows(cuda_device):
     assert mx <= MAX_ABS and mean <= MEAN_ABS, (mx, mean)
 
 
-def test_neighbour_rows_behind_a_sequence_end_are_ignored(cuda_device):
+@pytest.mark.parametrize("max_k", SHAPES)
+def test_neighbour_rows_behind_a_sequence_end_are_ignored(cuda_device, max_k):
     """The last key/value tile of a packed sequence also holds the first rows of the next
     sequence; NaN/Inf there must not leak (the reference's loads are predicated)."""
     g = torch.Generator().manual_seed(93)
@@ -177,7 +190,7 @@ def test_neighbour_rows_behind_a_sequence_end_are_ignored(cuda_device):
     kp[100:160] = float("nan")   # poison the middle sequence: its own rows become NaN, its
     vp[100:160] = float("inf")   # neighbours must not notice
     out = tch_cuda.flash_attn_varlen(q.to(cuda_device), kp.to(cuda_device), vp.to(cuda_device),
-                                     cu.to(cuda_device), cu.to(cuda_device), 200, 200, scale, True).cpu()
+                                     cu.to(cuda_device), cu.to(cuda_device), 200, max_k or 200, scale, True).cpu()
     keep = torch.cat([torch.arange(0, 100), torch.arange(160, 360)])
     assert torch.isfinite(out[keep].float()).all()
     mx, mean = O.error_stats(out[keep], want[keep])

@@ -53,12 +53,15 @@ def _oracle(q, kc, vc, cu_q, lens_k, slots, scale, hkv):
     ([512] * 3, [1536] * 3, 8, 2, False),               # config-5 variant: 1024 tokens already cached
     ([5, 64, 200], [77, 1000, 215], 4, 1, True),        # chunked prefill, odd lengths
 ])
-def test_paged_prefill_matches_oracle_and_packed_kernel(cuda_device, lens_q, lens_k, hq, hkv, poison):
+@pytest.mark.parametrize("max_k", [pytest.param(None, id="shape_by_length"), pytest.param(4096, id="two_tile_shape")])
+def test_paged_prefill_matches_oracle_and_packed_kernel(cuda_device, lens_q, lens_k, hq, hkv, poison, max_k):
+    """max_k: the upper bound on the context length the caller passes; it selects the kernel shape
+    (one query tile per CTA up to 1024 keys, two above), so a loose bound runs the other shape."""
     dev = cuda_device
     q, kc, vc, table, cu_q, cl, slots = _case(dev, 900 + hq, lens_q, lens_k, hq, hkv, poison)
     scale = 1.0 / 128 ** 0.5
     out = tch_cuda.flash_attn_varlen_paged(q, kc, vc, cu_q.to(dev), cl.to(dev), table.to(dev), max(lens_q),
-                                           max(lens_k), scale, True)
+                                           max_k or max(lens_k), scale, True)
     torch.cuda.synchronize()
     assert _lib.last_status() == 0
     want, k, v, cu_k = _oracle(q, kc, vc, cu_q, lens_k, slots, scale, hkv)
@@ -67,7 +70,7 @@ def test_paged_prefill_matches_oracle_and_packed_kernel(cuda_device, lens_q, len
     mx, mean = O.error_stats(got, want)
     assert mx <= MAX_ABS and mean <= MEAN_ABS, (mx, mean)
     packed = tch_cuda.flash_attn_varlen(q, k.to(dev), v.to(dev), cu_q.to(dev), cu_k.to(dev), max(lens_q),
-                                        max(lens_k), scale, True)
+                                        max_k or max(lens_k), scale, True)
     mx2, mean2 = O.error_stats(got, packed.cpu().float())
     assert mx2 <= 4e-3 and mean2 <= 1e-4, (mx2, mean2)  # same arithmetic, different staging
 
