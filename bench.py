@@ -76,12 +76,13 @@ def shared_config(n_gpus, step_bytes):
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
+    """Samples SM clock and throttle reasons through NVML (read-only) while a timed region runs:
+    `region(name)` opens a region, `region(None)` closes it; samples outside a region are dropped."""
 
-    def __init__(self, index, period=0.02):
+    def __init__(self, index, period=0.005):
         super().__init__(daemon=True)
         self.index, self.period = index, period
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.data, self.current, self.max_mhz = {}, None, None
         self._stop_evt = threading.Event()
         self.ok = False
         try:
@@ -94,6 +95,9 @@ class ClockSampler(threading.Thread):
         except Exception:
             self.ok = False
 
+    def region(self, name):
+        self.current = name
+
     def run(self):
         if not self.ok:
             return
@@ -105,24 +109,31 @@ class ClockSampler(threading.Thread):
             getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
         }
         while not self._stop_evt.is_set():
-            try:
-                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
-                r = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
-                for bit, name in names.items():
-                    if r & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
+            cur = self.current
+            if cur is not None:
+                try:
+                    mhz = int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                    r = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                    samples, reasons = self.data.setdefault(cur, ([], set()))
+                    samples.append(mhz)
+                    for bit, name in names.items():
+                        if r & bit:
+                            reasons.add(name)
+                except Exception:
+                    pass
             time.sleep(self.period)
 
     def stop(self):
         self._stop_evt.set()
         if self.is_alive():
             self.join(timeout=2)
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
-        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+    def summary(self, name):
+        samples, reasons = self.data.get(name, ([], set()))
+        if not samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(reasons), "samples": 0}
+        return {"sm_mhz": int(statistics.median(samples)), "sm_min_mhz": min(samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(reasons), "samples": len(samples)}
 
 
 def physical_gpu_index(local_rank):
@@ -462,6 +473,7 @@ def run_ours(args):
         runs = [(lambda i=i: step(i)) for i in range(n_graphs)]
     for i in range(3 * n_graphs):
         runs[i % n_graphs]()
+    sampler.region("decode")
     ms_total = R.max_over_ranks(timed_steps(runs, args.steps, profile=True)[0])
     ms_step = ms_total / args.steps
 
@@ -478,6 +490,7 @@ def run_ours(args):
     for i in range(3 * n_graphs):
         a_runs[i % n_graphs]()
     att_ms = R.max_over_ranks(timed_steps(a_runs, args.steps)[0]) / args.steps
+    sampler.region(None)
     status = _lib.last_status()
     if status != 0:
         raise SystemExit("device status word is %d after the timed region" % status)
@@ -708,6 +721,7 @@ def run_ours(args):
         pgather(pstep())
     R.barrier()
     k_ms = []
+    sampler.region("prefill")
     ev0.record()
     for _ in range(p_steps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -720,7 +734,9 @@ def run_ours(args):
     R.barrier()
     p_ms = R.max_over_ranks(ev0.elapsed_time(ev1)) / p_steps
     p_kernel_ms = R.max_over_ranks(sum(a.elapsed_time(b) for a, b in k_ms) / p_steps)
-    clocks = sampler.stop()
+    sampler.region(None)
+    sampler.stop()
+    clocks = sampler.summary("decode")
     p_flops_local = pw.flops()
     p_tflops = p_flops_local * world / (p_ms * 1e-3) / 1e12
     p_kernel_tflops = p_flops_local / (p_kernel_ms * 1e-3) / 1e12
@@ -819,6 +835,7 @@ def run_ours(args):
                          "frac_of_burst_peak": p_kernel_tflops / peaks["bf16_tflops"],
                          "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "launch_ms": p_kernel_ms,
                          "traffic": PREFILL_TRAFFIC_BYTES.get(world)},
+            "clocks": sampler.summary("prefill"),
         },
     }
     if cpu_baseline is not None:
