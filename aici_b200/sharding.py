@@ -112,6 +112,9 @@ def exchange_bytes(payload: bytes, group=None) -> List[bytes]:
     return [bytes(x) for x in out]
 
 
+HANDLE_BYTES = 128  # AICI_PEER_HANDLE_BYTES
+
+
 class _DevicePointer:
     """Lets torch view raw device memory (CUDA array interface, int16 elements)."""
 
@@ -139,7 +142,7 @@ class PeerMemory:
         self._own = ctypes.c_void_p(0)
         self._opened: List[int] = []
         self.ptrs: List[int] = []
-        handle = (ctypes.c_ubyte * 64)()
+        handle = (ctypes.c_ubyte * HANDLE_BYTES)()
         err: Optional[str] = None
         with torch.cuda.device(self.device):
             try:
@@ -147,10 +150,13 @@ class PeerMemory:
                     ctypes.c_size_t(self.nbytes), ctypes.byref(self._own), handle))
             except _lib.AiciError as e:
                 err = str(e)
+            # bytes 4..7 of a handle say how the block is shared (1: virtual-memory allocation through
+            # a duplicated file descriptor, 2: CUDA IPC handle of a cudaMalloc block)
+            self.kind = int.from_bytes(bytes(handle)[4:8], "little") if err is None else 0
             # every rank takes part in the exchange even if its own allocation failed, so that
             # nobody waits for a rank that has already given up
-            handles = exchange_bytes(bytes(handle) if err is None else b"\0" * 64, self.group)
-            if err is None and any(h == b"\0" * 64 for h in handles):
+            handles = exchange_bytes(bytes(handle) if err is None else b"\0" * HANDLE_BYTES, self.group)
+            if err is None and any(h == b"\0" * HANDLE_BYTES for h in handles):
                 err = "another rank could not allocate its peer buffer"
             if err is None:
                 for r, h in enumerate(handles):
@@ -160,7 +166,7 @@ class PeerMemory:
                     out = ctypes.c_void_p(0)
                     try:
                         _lib.check("aici_peer_open", _lib.lib().aici_peer_open(
-                            (ctypes.c_ubyte * 64).from_buffer_copy(h), ctypes.byref(out)))
+                            (ctypes.c_ubyte * HANDLE_BYTES).from_buffer_copy(h), ctypes.byref(out)))
                     except _lib.AiciError as e:
                         err = str(e)
                         break

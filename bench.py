@@ -404,13 +404,14 @@ def run_ours(args):
     pools = [(w.key_cache, w.value_cache)] + [(w.key_cache.clone(), w.value_cache.clone())
                                               for _ in range(n_pools - 1)]
     fused = world > 1 and args.gather == "fused"
-    pg, fused_fallback = None, None
+    pg, fused_fallback, peer_kind = None, None, 0
     if fused:
         # peer-mapped output buffers through the library's own calls (CUDA IPC); if any rank cannot
         # set them up, every rank falls back to the NCCL gather (and the JSON line says so)
         try:
             pg = sharding.PeerGather(S, hq_total, 128, dev, buffers=2)
             pg.barrier()
+            peer_kind = pg.mem.kind
         except Exception as e:  # noqa: BLE001
             fused_fallback = "%s: %s" % (type(e).__name__, str(e)[:160])
             fused, pg = False, None
@@ -798,8 +799,10 @@ def run_ours(args):
             "bytes_streamed_per_gpu_per_step": decode_bytes_local,
             "collective": ("none" if world == 1 else
                            "fused: the decode call stores head outputs into every rank's buffer over NVLink "
-                           "(buffers mapped with the library's CUDA-IPC calls, two used in turn) and its last "
-                           "kernel is the ranks' barrier" if fused else
+                           "(buffers mapped with the library's own peer-memory calls, %s; two used in turn) and "
+                           "its last kernel is the ranks' barrier" % (
+                               {1: "virtual-memory allocations shared by file descriptor",
+                                2: "cudaMalloc blocks shared by CUDA IPC handles"}.get(peer_kind, "?")) if fused else
                            "nccl all_gather of head outputs" +
                            (" (fused gather unavailable: %s)" % fused_fallback if fused_fallback else "")),
         },

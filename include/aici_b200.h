@@ -264,14 +264,17 @@ char *aici_paged_attention_v1_peers_barrier(void *const *outs, void *const *flag
 /* Peer-mapped device memory without libtorch or NCCL (no counterpart in the reference, which is
  * single-GPU; the hook this serves is the per-rank kv-head count of
  * rllm-cuda/src/llm/config.rs:30-36, 49-51).  One process per GPU:
- *   owner : aici_peer_alloc(bytes, &ptr, handle)  -- cudaMalloc, zero-filled, 64-byte IPC handle
+ *   owner : aici_peer_alloc(bytes, &ptr, handle)  -- zero-filled device memory + a 128-byte handle
  *   caller: moves the handle bytes to the other processes over any channel it has
- *   peers : aici_peer_open(handle, &ptr)          -- maps the owner's buffer, peer access enabled
+ *   peers : aici_peer_open(handle, &ptr)          -- maps the owner's buffer into this process
+ * The memory is a CUDA virtual-memory allocation (2 MB pages) shared through a file descriptor that
+ * the peer duplicates with pidfd_getfd; where that is not possible, cudaMalloc with a CUDA IPC
+ * handle.  The handle says which; processes must share a PID namespace (one container).
  * The pointers go into outs[] / flag_ptrs[] above (index = owner's rank; a rank's own buffer is the
  * pointer aici_peer_alloc gave it).  Tear-down: every peer aici_peer_close()s its mappings, the
  * processes meet (the caller's own barrier), then each owner aici_peer_free()s.  These four calls
  * allocate or map memory and synchronise the device: set-up time only, never inside a step. */
-#define AICI_PEER_HANDLE_BYTES 64
+#define AICI_PEER_HANDLE_BYTES 128
 char *aici_peer_alloc(size_t bytes, void **ptr_out, void *handle_out);
 char *aici_peer_open(const void *handle, void **ptr_out);
 char *aici_peer_close(void *ptr);
