@@ -26,6 +26,7 @@ EXPORTS = (
     "aici_paged_attention_v2",
     "aici_paged_attention_v1_static",
     "aici_mha_varlen_fwd",
+    "aici_mha_varlen_fwd_shape",
     "aici_mha_varlen_paged_fwd",
     "aici_paged_attention_v1_peers",
     "aici_mha_varlen_fwd_peers",

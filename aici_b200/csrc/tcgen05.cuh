@@ -188,4 +188,105 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 
+// ---- CTA pairs (cta_group::2): one MMA spans the tensor cores of two SMs -----------------------------
+// A cluster of two CTAs on neighbouring SMs.  One thread of the leader CTA (cluster rank 0) issues
+// each MMA for both: M = 256 rows, 128 in each CTA's tensor memory; the A operand comes from each
+// CTA's own shared or tensor memory, the B operand's N extent is split, half of it from each CTA's
+// shared memory (descriptors hold CTA-relative addresses, the same in both).  Tensor memory is
+// allocated, relinquished and freed by the same warp of BOTH CTAs with the cta_group::2 forms.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// All threads of all CTAs of the cluster meet; orders shared-memory accesses across the CTAs.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrives on the barrier at the same shared-memory offset in CTA `cta` of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t *bar, uint32_t cta) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(cta));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait on a barrier that another CTA of the cluster arrives on (acquire at cluster scope);
+// gives up like mbar_wait_abortable.
+__device__ __forceinline__ bool mbar_wait_abortable_cluster(uint64_t *bar, uint32_t parity, unsigned int *st) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  unsigned polls = 0;
+  unsigned long long *stamp = reinterpret_cast<unsigned long long *>(st + 2);
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++polls & 255u) == 0u) {
+      const unsigned long long seen = *reinterpret_cast<volatile unsigned long long *>(stamp);
+      if (seen != 0ull && global_timer_ns() - seen < 2000000000ull) return false;
+      if (clock64() - t0 > (1ll << 31)) {
+        set_status(st, AICI_STATUS_WAIT_TIMEOUT);
+        atomicExch(stamp, global_timer_ns());
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Arrives once on the barrier at this shared-memory offset in every CTA of cta_mask when all MMAs
+// issued so far by this thread have completed.  (A commit with cluster multicast is a barrier
+// signal, not a load; the TMA loads of the pair kernel carry no multicast.)
+__device__ __forceinline__ void tc_commit_pair(uint64_t *bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"(cta_mask)
+               : "memory");
+}
+// D[tmem, both CTAs] (+)= A[smem, each CTA's own] * B[smem, N halves from the two CTAs]
+__device__ __forceinline__ void umma_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem, both CTAs] (+)= A[tmem, each CTA's own] * B[smem, N halves from the two CTAs]
+__device__ __forceinline__ void umma_ts_pair(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 }  // namespace aici

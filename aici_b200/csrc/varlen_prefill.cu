@@ -32,23 +32,35 @@ constexpr int kBN = 128;               // keys per tile
 constexpr int kHD = 128;               // head size
 constexpr int kPanelBytes = 128 * 128; // [128 rows][64 bf16] = one 128B-swizzled panel
 constexpr int kTileBytes = 2 * kPanelBytes;
-constexpr int kMaxKvStages = 4;        // ring of K/V tiles (K_j and V_j alternate)
+constexpr int kMaxKvStages = 6;        // ring of K/V tiles (K_j and V_j alternate)
 
-// Two shapes of the same kernel.  kTiles = 2 (long sequences): one CTA per SM owns two query tiles
-// that share their K/V tiles; all 512 TMEM columns (S0/P0 [0,128) S1/P1 [128,256) O0 [256,384)
-// O1 [384,512)), a 4-stage K/V ring, 8 softmax warps.  kTiles = 1 (short sequences): one query tile,
-// 256 TMEM columns (S/P [0,128) O [128,256)), a 2-stage ring, 4 softmax warps -- half the shared
-// memory and half the tensor memory, so TWO CTAs share an SM and one CTA's fill (barriers, TMEM
-// allocation, first loads) and drain (epilogue, stores, exit) run under the other's MMAs.
-template <int kTiles>
+// Three shapes of the same kernel.
+//   1  one query tile per CTA (short sequences): 256 TMEM columns (S/P [0,128) O [128,256)), a 2-stage
+//      K/V ring, 4 softmax warps -- half the shared and tensor memory of shape 2, so TWO CTAs share an
+//      SM and one CTA's fill (barriers, TMEM allocation, first loads) and drain (epilogue, stores,
+//      exit) run under the other's MMAs.
+//   2  two query tiles per CTA that share their K/V tiles (long sequences): all 512 TMEM columns
+//      (S0/P0 [0,128) S1/P1 [128,256) O0 [256,384) O1 [384,512)), a 4-stage ring, 8 softmax warps.
+//   3  shape 2 on a PAIR of CTAs (a cluster of two on neighbouring SMs) that work on four query heads
+//      of one kv head: every MMA is one cta_group::2 instruction over both SMs (M = 256, 128 rows in
+//      each CTA's tensor memory) and its B operand is split between them -- each CTA loads and holds
+//      only half of every key tile (64 keys) and half of every value tile (64 of the 128 columns).
+//      An SS-form S = Q K^T step then reads 6 KB of shared memory per SM instead of 8 KB and a P V
+//      step 2 KB instead of 4 KB; shared-memory bandwidth into the tensor core (about 64 B/clk) is
+//      what holds shape 2 back.  The leader CTA issues; the other CTA's issuer warp relays "my half
+//      has landed" to it; completion comes back to both through multicast commits.
+template <int kShape>
 struct PrefillCfg {
-  static constexpr int kStages = kTiles == 2 ? 4 : 2;
+  static constexpr int kTiles = kShape == 1 ? 1 : 2;
+  static constexpr bool kPair = kShape == 3;
+  static constexpr int kStages = kShape == 1 ? 2 : (kShape == 2 ? 4 : 6);
+  static constexpr int kStageBytes = kPair ? kTileBytes / 2 : kTileBytes;
   static constexpr int kSoftmaxWarps = 4 * kTiles;
   static constexpr int kProducerWarp = 4 * kTiles;
   static constexpr int kMmaWarp = 4 * kTiles + 1;
   static constexpr int kThreads = (4 * kTiles + 2) * 32;
   static constexpr uint32_t kCols = 256u * kTiles;
-  static constexpr int kSmemBytes = (kTiles + kStages) * kTileBytes + 1024 /*align*/ + 256 /*PrefillSmem*/;
+  static constexpr int kSmemBytes = kTiles * kTileBytes + kStages * kStageBytes + 1024 /*align*/ + 512 /*PrefillSmem*/;
   static constexpr int kCtasPerSm = kTiles == 2 ? 1 : 2;
 };
 constexpr float kRescaleThreshold = 8.f;  // log2 units: the running reference moves once a score exceeds it by this
@@ -84,6 +96,7 @@ struct OutMaps {
 
 struct PrefillSmem {
   uint64_t q_full[2], kv_full[kMaxKvStages], kv_empty[kMaxKvStages], s_full[2], p_ready[2], o_full[2], staged[2], drain;
+  uint64_t q_peer[2], kv_peer[kMaxKvStages];  // CTA pairs: the leader's view of "the other CTA's half has landed"
   uint32_t tmem_base;
   uint32_t aborted;
 };
@@ -112,20 +125,26 @@ __device__ __forceinline__ void zero_rows(const PrefillParams &p, int q0, const 
 //   2 KB between 8-token groups); a value tile is 8 blocks of [128 d][16 tokens] loaded with the
 //   32-byte swizzle, one K = 16 MMA per block.  Value columns past the sequence end are zeroed in
 //   shared memory before P V (cache slots there may hold anything, NaN included).
-template <bool kPaged, int kTiles>
-__global__ void __launch_bounds__(PrefillCfg<kTiles>::kThreads, PrefillCfg<kTiles>::kCtasPerSm)
+template <bool kPaged, int kShape>
+__global__ void __launch_bounds__(PrefillCfg<kShape>::kThreads, PrefillCfg<kShape>::kCtasPerSm)
 varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v,
                       const __grid_constant__ OutMaps tmap_o, const PrefillParams p) {
-  using Cfg = PrefillCfg<kTiles>;
+  using Cfg = PrefillCfg<kShape>;
+  constexpr int kTiles = Cfg::kTiles;
+  constexpr bool kPair = Cfg::kPair;
+  static_assert(!(kPair && kPaged), "the CTA-pair shape reads packed K/V only");
   constexpr int kKvStages = Cfg::kStages;
+  constexpr int kStageBytes = Cfg::kStageBytes;
   constexpr int kPrefillThreads = Cfg::kThreads;
   constexpr uint32_t kTmemCols = Cfg::kCols;
   constexpr uint32_t kOCol = 128u * kTiles;  // first column of O0
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int b = blockIdx.z;
+  // shape 1 orders its grid (head, sequence, row tile) so that the row tile is the slowest index: all
+  // the longest tiles of the batch start first and the one-key-tile CTAs fill the tail
+  const int b = kTiles == 1 ? blockIdx.y : blockIdx.z;
   const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
   int k0 = 0, lk = 0;
   if (kPaged) {
@@ -146,9 +165,14 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   {
     int mb[2], hh[2];
     if (kTiles == 1) {
-      mb[0] = n_mblocks - 1 - (int)blockIdx.x;
+      mb[0] = n_mblocks - 1 - (int)blockIdx.z;
       mb[1] = -1;  // no second tile
-      hh[0] = hh[1] = (int)blockIdx.y;
+      hh[0] = hh[1] = (int)blockIdx.x;
+    } else if (kPair) {
+      // clusters of two CTAs along x: CTA x = 2m + r holds heads 4y + 2r and 4y + 2r + 1 of row tile m
+      mb[0] = mb[1] = n_mblocks - 1 - (int)(blockIdx.x >> 1);
+      hh[0] = 4 * (int)blockIdx.y + 2 * (int)(blockIdx.x & 1);
+      hh[1] = hh[0] + 1;
     } else if (p.pair_heads) {
       mb[0] = mb[1] = n_mblocks - 1 - (int)blockIdx.x;
       hh[0] = 2 * (int)blockIdx.y;
@@ -180,15 +204,19 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t *sQ = smem;                       // two tiles
-  uint8_t *sKV = smem + kTiles * kTileBytes;     // kKvStages tiles
-  PrefillSmem *sh = reinterpret_cast<PrefillSmem *>(smem + (kTiles + kKvStages) * kTileBytes);
+  uint8_t *sKV = smem + kTiles * kTileBytes;     // kKvStages stages
+  PrefillSmem *sh = reinterpret_cast<PrefillSmem *>(smem + kTiles * kTileBytes + kKvStages * kStageBytes);
+  // CTA pairs: rank 0 of the cluster is the leader (issues the MMAs of both CTAs)
+  const uint32_t pair_rank = kPair ? cluster_ctarank() : 0u;
+  const bool leader = pair_rank == 0u;
 
   if (tid == 0) {
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
       mbar_init(&sh->q_full[t], 1);
       mbar_init(&sh->s_full[t], 1);
-      mbar_init(&sh->p_ready[t], 4);
+      mbar_init(&sh->p_ready[t], kPair ? 8 : 4);  // pairs: the softmax warps of both CTAs report to the leader
+      mbar_init(&sh->q_peer[t], 1);
       mbar_init(&sh->o_full[t], 1);
       mbar_init(&sh->staged[t], 4);
     }
@@ -196,17 +224,24 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     for (int s = 0; s < kKvStages; ++s) {
       mbar_init(&sh->kv_full[s], 1);
       mbar_init(&sh->kv_empty[s], 1);
+      mbar_init(&sh->kv_peer[s], 1);
     }
     mbar_init(&sh->drain, 1);
     sh->aborted = 0;
     fence_mbar_init();
   }
   if (warp == Cfg::kMmaWarp) {
-    tmem_alloc(&sh->tmem_base, kTmemCols);
-    tmem_relinquish();
+    if (kPair) {
+      tmem_alloc_pair(&sh->tmem_base, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&sh->tmem_base, kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (kPair) cluster_sync_all();  // the other CTA's barriers exist before anything arrives on them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
 
@@ -270,65 +305,136 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       for (int i = 0; i < 2 * nmax; ++i) {  // i even: K_{i/2}, i odd: V_{i/2}
         const int stage = i % kKvStages;
         if (!mbar_wait_abortable(&sh->kv_empty[stage], (((uint32_t)i / kKvStages) & 1u) ^ 1u, p.status)) break;
-        uint8_t *dst = sKV + stage * kTileBytes;
+        uint8_t *dst = sKV + stage * kStageBytes;
         const CUtensorMap *tm = (i & 1) ? &tmap_v : &tmap_k;
-        mbar_expect_tx(&sh->kv_full[stage], kTileBytes);
-        tma_load_3d(dst, tm, 0, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
-        tma_load_3d(dst + kPanelBytes, tm, 64, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
+        mbar_expect_tx(&sh->kv_full[stage], kStageBytes);
+        if (!kPair) {
+          tma_load_3d(dst, tm, 0, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
+          tma_load_3d(dst + kPanelBytes, tm, 64, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
+        } else if (i & 1) {
+          // this CTA's half of the value tile: 64 of the 128 columns, all 128 tokens (one panel)
+          tma_load_3d(dst, tm, 64 * (int)pair_rank, hk, k0 + (i >> 1) * kBN, &sh->kv_full[stage]);
+        } else {
+          // this CTA's half of the key tile: 64 of the 128 tokens (tmap_k's box is 64 rows high),
+          // two panels of 64 columns
+          const int row = k0 + (i >> 1) * kBN + 64 * (int)pair_rank;
+          tma_load_3d(dst, tm, 0, hk, row, &sh->kv_full[stage]);
+          tma_load_3d(dst + kPanelBytes / 2, tm, 64, hk, row, &sh->kv_full[stage]);
+        }
       }
     }
-  } else if (warp == Cfg::kMmaWarp) {
-    // ---------------------------------------------------------------- MMA issuer -------------
-    constexpr uint32_t idesc_s = idesc_bf16(kBM, kBN, false);
-    constexpr uint32_t idesc_pv = idesc_bf16(kBM, kHD, !kPaged);  // packed V: MN-major; cache V: K-major
+  } else if (warp == Cfg::kMmaWarp && kPair && !leader) {
+    // ---------------------------------------------------------------- relay (pairs, second CTA) --
+    // The leader issues the MMAs that read this CTA's shared memory too; it learns from this warp,
+    // in consumption order, that this CTA's Q tiles and K/V halves have landed.
     bool ok = true;
     auto wait = [&](uint64_t *bar, uint32_t parity) {
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait_abortable(bar, parity, p.status));
       return ok;
     };
-    auto wait_kv = [&](int i) { return wait(&sh->kv_full[i % kKvStages], ((uint32_t)i / kKvStages) & 1u); };
+    for (int t = 0; t < 2 && ok; ++t) {
+      if (tiles[t].n_tiles > 0 && wait(&sh->q_full[t], 0)) {
+        fence_proxy_async_smem();
+        if (lane == 0) mbar_arrive_cluster(&sh->q_peer[t], 0);
+      }
+    }
+    for (int i = 0; ok && i < 2 * nmax; ++i) {
+      const int stage = i % kKvStages;
+      if (!wait(&sh->kv_full[stage], ((uint32_t)i / kKvStages) & 1u)) break;
+      const int j = i >> 1;
+      if ((i & 1) && lk - j * kBN < kBN) {
+        // value rows behind the end of the sequence are cleared (see the leader's copy of this loop)
+        const int valid = lk - j * kBN;
+        uint8_t *vt = sKV + stage * kStageBytes;
+        for (int idx = valid * 8 + lane; idx < kBN * 8; idx += 32)
+          *reinterpret_cast<uint4 *>(vt + (idx >> 3) * 128 + (idx & 7) * 16) = make_uint4(0, 0, 0, 0);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(&sh->kv_peer[stage], 0);
+    }
+  } else if (warp == Cfg::kMmaWarp) {
+    // ---------------------------------------------------------------- MMA issuer -------------
+    constexpr uint32_t idesc_s = idesc_bf16(kPair ? 2 * kBM : kBM, kBN, false);
+    constexpr uint32_t idesc_pv = idesc_bf16(kPair ? 2 * kBM : kBM, kHD, !kPaged);  // packed V: MN-major; cache V: K-major
+    constexpr int kKPanel = kPair ? kPanelBytes / 2 : kPanelBytes;  // one 64-column panel of a key (half) tile
+    bool ok = true;
+    auto wait = [&](uint64_t *bar, uint32_t parity) {
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait_abortable(bar, parity, p.status));
+      return ok;
+    };
+    // barriers another CTA arrives on: acquire at cluster scope
+    auto wait_cluster = [&](uint64_t *bar, uint32_t parity) {
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait_abortable_cluster(bar, parity, p.status));
+      return ok;
+    };
+    auto wait_q = [&](int t) {
+      wait(&sh->q_full[t], 0);
+      if (kPair) wait_cluster(&sh->q_peer[t], 0);
+      return ok;
+    };
+    auto wait_kv = [&](int i) {
+      wait(&sh->kv_full[i % kKvStages], ((uint32_t)i / kKvStages) & 1u);
+      if (kPair) wait_cluster(&sh->kv_peer[i % kKvStages], ((uint32_t)i / kKvStages) & 1u);
+      return ok;
+    };
+    auto wait_p = [&](int t, int j) {
+      return kPair ? wait_cluster(&sh->p_ready[t], (uint32_t)j & 1u) : wait(&sh->p_ready[t], (uint32_t)j & 1u);
+    };
+    auto commit = [&](uint64_t *bar) {
+      if (kPair) tc_commit_pair(bar, 3);
+      else tc_commit(bar);
+    };
     // S_t = Q_t K^T.  Q, K: K-major, rows of 128 B, 8-row groups 1024 B apart, two 64-column panels.
     auto issue_s = [&](int t, int i_k) {
       tc_fence_after();
       if (lane == 0) {
         const uint64_t qdesc = smem_desc_sw128(smem_u32(sQ + t * kTileBytes), 16, 1024);
-        const uint32_t kaddr = smem_u32(sKV + (i_k % kKvStages) * kTileBytes);
+        const uint32_t kaddr = smem_u32(sKV + (i_k % kKvStages) * kStageBytes);
         const uint64_t kdesc = kPaged ? smem_desc(kaddr, 128, 2048, 0) : smem_desc_sw128(kaddr, 16, 1024);
 #pragma unroll
         for (int ks = 0; ks < kHD / 16; ++ks) {
           const uint64_t adv = (uint64_t)(((ks >> 2) * kPanelBytes + (ks & 3) * 32) >> 4);
-          const uint64_t kadv = kPaged ? (uint64_t)((ks * 256) >> 4) : adv;
-          umma_ss(tmem_base + t * 128, qdesc + adv, kdesc + kadv, idesc_s, ks > 0 ? 1u : 0u);
+          const uint64_t kadv = kPaged ? (uint64_t)((ks * 256) >> 4)
+                                       : (uint64_t)(((ks >> 2) * kKPanel + (ks & 3) * 32) >> 4);
+          if (kPair) umma_ss_pair(tmem_base + t * 128, qdesc + adv, kdesc + kadv, idesc_s, ks > 0 ? 1u : 0u);
+          else umma_ss(tmem_base + t * 128, qdesc + adv, kdesc + kadv, idesc_s, ks > 0 ? 1u : 0u);
         }
-        tc_commit(&sh->s_full[t]);
+        commit(&sh->s_full[t]);
       }
       __syncwarp();
     };
     // O_t += P_t V.  V as B operand: N (= d) contiguous, 64 d per swizzle atom, second atom one
-    // panel further (leading offset), 8-token groups 1024 B apart (stride offset).
+    // panel further (leading offset), 8-token groups 1024 B apart (stride offset).  In a CTA pair
+    // each CTA holds one atom (its 64 columns).
     auto issue_pv = [&](int t, int i_v, bool first, bool last) {
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t vaddr = smem_u32(sKV + (i_v % kKvStages) * kTileBytes);
+        const uint32_t vaddr = smem_u32(sKV + (i_v % kKvStages) * kStageBytes);
         // packed: one MN-major tile, a K step = 16 token rows of 128 B; cache: one block per K step,
         // rows (d) of 32 B with the 32-byte swizzle, 8-row groups 256 B apart
         const uint64_t vdesc = kPaged ? smem_desc(vaddr, 16, 256, 6) : smem_desc_sw128(vaddr, kPanelBytes, 1024);
         const uint32_t vstep = kPaged ? 4096u : 2048u;
 #pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks)
-          umma_ts(tmem_base + kOCol + t * 128, tmem_base + t * 128 + 8 * ks, vdesc + (uint64_t)((ks * vstep) >> 4),
-                  idesc_pv, (!first || ks > 0) ? 1u : 0u);
-        if (last) tc_commit(&sh->o_full[t]);
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          if (kPair)
+            umma_ts_pair(tmem_base + kOCol + t * 128, tmem_base + t * 128 + 8 * ks,
+                         vdesc + (uint64_t)((ks * vstep) >> 4), idesc_pv, (!first || ks > 0) ? 1u : 0u);
+          else
+            umma_ts(tmem_base + kOCol + t * 128, tmem_base + t * 128 + 8 * ks, vdesc + (uint64_t)((ks * vstep) >> 4),
+                    idesc_pv, (!first || ks > 0) ? 1u : 0u);
+        }
+        if (last) commit(&sh->o_full[t]);
       }
       __syncwarp();
     };
     auto release = [&](int i) {
-      if (lane == 0) tc_commit(&sh->kv_empty[i % kKvStages]);
+      if (lane == 0) commit(&sh->kv_empty[i % kKvStages]);
       __syncwarp();
     };
 
-    if (nt0 > 0) wait(&sh->q_full[0], 0);
-    if (nt1 > 0) wait(&sh->q_full[1], 0);
+    if (nt0 > 0) wait_q(0);
+    if (nt1 > 0) wait_q(1);
     if (wait_kv(0)) {
       if (nt0 > 0) issue_s(0, 0);
       if (nt1 > 0) issue_s(1, 0);
@@ -341,7 +447,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // last tile of the sequence: zero the value columns of tokens >= lk (generic-proxy stores,
         // made visible to the tensor core with a proxy fence)
         const int valid = lk - j * kBN;
-        uint8_t *vt = sKV + (i_v % kKvStages) * kTileBytes;
+        uint8_t *vt = sKV + (i_v % kKvStages) * kStageBytes;
         for (int bi = valid / 16; bi < 8; ++bi) {
           uint8_t *vb = vt + bi * 4096;
           const int first = max(0, valid - bi * 16);
@@ -360,19 +466,21 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // Packed layout, last tile of the sequence: the rows behind it belong to the next sequence
         // (or were zero-filled past the end of the tensor).  Their probabilities are 0, but 0 x NaN
         // is NaN, so the rows are cleared as the reference's predicated loads clear them
-        // (flash_fwd_kernel.h, Clear_OOB_MN).  A token row is 128 B in each of the two panels; the
-        // swizzle only permutes bytes inside a row.
+        // (flash_fwd_kernel.h, Clear_OOB_MN).  A token row is 128 B in each panel (two panels; one
+        // in a CTA pair, where the other CTA clears its own); the swizzle only permutes bytes
+        // inside a row.
         const int valid = lk - j * kBN;
-        uint8_t *vt = sKV + (i_v % kKvStages) * kTileBytes;
-        for (int idx = valid * 16 + lane; idx < kBN * 16; idx += 32) {
-          const int r = idx >> 4, c = idx & 15;  // row, 16-byte piece (8 per panel)
+        uint8_t *vt = sKV + (i_v % kKvStages) * kStageBytes;
+        constexpr int kPieces = kPair ? 8 : 16;  // 16-byte pieces of a token row held by this CTA
+        for (int idx = valid * kPieces + lane; idx < kBN * kPieces; idx += 32) {
+          const int r = idx / kPieces, c = idx % kPieces;
           *reinterpret_cast<uint4 *>(vt + (c >> 3) * kPanelBytes + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async_smem();
         __syncwarp();
       }
       if (j < nt0) {
-        if (!wait(&sh->p_ready[0], (uint32_t)j & 1u)) break;
+        if (!wait_p(0, j)) break;
         issue_pv(0, i_v, j == 0, j == nt0 - 1);
       }
       if (j + 1 < nt0) {
@@ -380,7 +488,7 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         issue_s(0, i_kn);
       }
       if (j < nt1) {
-        if (!wait(&sh->p_ready[1], (uint32_t)j & 1u)) break;
+        if (!wait_p(1, j)) break;
         issue_pv(1, i_v, j == 0, j == nt1 - 1);
       }
       release(i_v);
@@ -601,7 +709,10 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->p_ready[t]);
+      if (lane == 0) {
+        if (kPair && !leader) mbar_arrive_cluster(&sh->p_ready[t], 0);  // the leader issues this CTA's P V too
+        else mbar_arrive(&sh->p_ready[t]);
+      }
     }
 
 
@@ -671,15 +782,21 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
   // ---- teardown ------------------------------------------------------------------------------
   tc_fence_before();
-  __syncthreads();
+  __syncwarp();
+  if (warp == Cfg::kMmaWarp && sh->aborted) {
+    // bounded wait for whatever the tensor pipe still owes before the columns are released (only
+    // the issuing CTA sets the flag)
+    if (lane == 0) tc_commit(&sh->drain);
+    __syncwarp();
+    mbar_wait(&sh->drain, 0, p.status);
+  }
+  // pairs: neither CTA may leave (its shared and tensor memory are operands of the other's MMAs)
+  // before both are through
+  if (kPair) cluster_sync_all();
+  else __syncthreads();
   if (warp == Cfg::kMmaWarp) {
-    if (sh->aborted) {
-      // bounded wait for whatever the tensor pipe still owes before the columns are released
-      if (lane == 0) tc_commit(&sh->drain);
-      __syncwarp();
-      mbar_wait(&sh->drain, 0, p.status);
-    }
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (kPair) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -753,14 +870,15 @@ struct TmapCache {
 };
 static TmapCache g_tmap_cache;
 
-// [tokens, heads, 128] bf16 with element strides -> 3-D map, box = 64 (d) x 1 (head) x 128 (tokens).
+// [tokens, heads, 128] bf16 with element strides -> 3-D map, box = 64 (d) x 1 (head) x box_rows (tokens;
+// 128, or 64 for the key half-tiles of the CTA-pair shape).
 static char *make_tmap(const char *fn, CUtensorMap *map, const void *base, int64_t tokens, int heads,
-                       int64_t tok_stride, int64_t head_stride) {
-  const TmapKey key = {base, tokens, heads, tok_stride, head_stride, 0};
+                       int64_t tok_stride, int64_t head_stride, int box_rows = kBM) {
+  const TmapKey key = {base, tokens, heads, tok_stride, head_stride, box_rows == kBM ? 0 : 3};
   if (g_tmap_cache.find(key, map)) return nullptr;
   cuuint64_t dims[3] = {(cuuint64_t)kHD, (cuuint64_t)heads, (cuuint64_t)tokens};
   cuuint64_t strides[2] = {(cuuint64_t)head_stride * 2, (cuuint64_t)tok_stride * 2};
-  cuuint32_t box[3] = {64, 1, (cuuint32_t)kBM};
+  cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
   if (char *e = make_tmap_nd(fn, map, base, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
   g_tmap_cache.put(key, *map);
   return nullptr;
@@ -796,40 +914,92 @@ static char *make_cache_tmap(const char *fn, CUtensorMap *map, const void *base,
 #define AICI_PREFILL_ONE_TILE_MAX_K 1024
 #endif
 
-template <bool kPaged, int kTiles>
+template <bool kPaged, int kShape>
 static char *launch_prefill_shape(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
                                   const OutMaps &to, PrefillParams &p, int num_heads, int batch,
                                   int max_seqlen_q, cudaStream_t stream) {
-  using Cfg = PrefillCfg<kTiles>;
+  using Cfg = PrefillCfg<kShape>;
   static OncePerDevice once;
   if (char *e = once.run([]() -> char * {
-        AICI_CUDA(cudaFuncSetAttribute(varlen_prefill_kernel<kPaged, kTiles>,
+        AICI_CUDA(cudaFuncSetAttribute(varlen_prefill_kernel<kPaged, kShape>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         return nullptr;
       }))
     return e;
   const int mblocks = (max_seqlen_q + kBM - 1) / kBM;
   dim3 grid;
-  if (kTiles == 1) {
-    grid = dim3(mblocks, num_heads, batch);
+  if (Cfg::kTiles == 1) {
+    grid = dim3(num_heads, batch, mblocks);
+  } else if (Cfg::kPair) {
+    p.pair_heads = 1;
+    grid = dim3(2 * mblocks, num_heads / 4, batch);
   } else {
     // two tiles per CTA: two heads of one kv group when the group is even, else two row tiles
     p.pair_heads = (p.group % 2 == 0) ? 1 : 0;
     grid = dim3(p.pair_heads ? mblocks : (mblocks + 1) / 2, p.pair_heads ? num_heads / 2 : num_heads, batch);
   }
-  varlen_prefill_kernel<kPaged, kTiles><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, to, p);
-  AICI_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(Cfg::kThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (Cfg::kPair) {
+    // clusters of two CTAs along x: the pair works on four query heads of one kv head
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t le = cudaLaunchKernelEx(&cfg, varlen_prefill_kernel<kPaged, kShape>, tq, tk, tv, to, p);
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    int clusters = -1, max_size = -1;
+    cudaError_t e1 = cudaSuccess, e2 = cudaSuccess;
+    if (Cfg::kPair) {
+      e1 = cudaOccupancyMaxActiveClusters(&clusters, varlen_prefill_kernel<kPaged, kShape>, &cfg);
+      cudaLaunchConfig_t probe = cfg;
+      probe.attrs = nullptr;
+      probe.numAttrs = 0;
+      e2 = cudaOccupancyMaxPotentialClusterSize(&max_size, varlen_prefill_kernel<kPaged, kShape>, &probe);
+      cudaGetLastError();
+    }
+    return err("prefill launch (shape %d, grid %u x %u x %u, %d threads, %d bytes of shared memory) failed: %s "
+               "[active clusters %d (%s), largest cluster %d (%s)]",
+               kShape, grid.x, grid.y, grid.z, Cfg::kThreads, Cfg::kSmemBytes, cudaGetErrorString(le), clusters,
+               cudaGetErrorString(e1), max_size, cudaGetErrorString(e2));
+  }
+  return nullptr;
+}
+
+// Which shape a call takes.  `forced` = 0: by sequence length -- shape 1 up to
+// AICI_PREFILL_ONE_TILE_MAX_K keys, shape 2 above; the CTA-pair shape is never chosen by itself (on
+// the long-context benchmark it runs at 0.83 of shape 2: what it saves in shared-memory reads it
+// loses to the cross-SM hand-over between the softmax warps and the issuing thread).  forced = 1, 2,
+// 3: that shape, for tests and comparisons; 3 needs packed K/V and four query heads per kv head in
+// one CTA pair (group a multiple of 4).
+static char *pick_shape(const char *fn, int forced, bool paged, int num_heads, int group, int max_seqlen_k,
+                        int *shape) {
+  AICI_CHECK(forced >= 0 && forced <= 3, "%s: shape must be 0 (automatic), 1, 2 or 3", fn);
+  AICI_CHECK(forced != 3 || (!paged && group % 4 == 0 && num_heads % 4 == 0),
+             "%s: the CTA-pair shape needs packed keys/values and a group size that is a multiple of 4", fn);
+  *shape = forced != 0 ? forced : (max_seqlen_k <= AICI_PREFILL_ONE_TILE_MAX_K ? 1 : 2);
   return nullptr;
 }
 
 template <bool kPaged>
-static char *launch_prefill(const char *fn, const CUtensorMap &tq, const CUtensorMap &tk,
-                            const CUtensorMap &tv, const OutMaps &to, PrefillParams &p, int num_heads,
-                            int batch, int max_seqlen_q, int max_seqlen_k, cudaStream_t stream) {
-  (void)fn;
+static char *launch_prefill(int shape, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
+                            const OutMaps &to, PrefillParams &p, int num_heads, int batch, int max_seqlen_q,
+                            cudaStream_t stream) {
   p.pair_heads = 0;
-  if (max_seqlen_k <= AICI_PREFILL_ONE_TILE_MAX_K)
+  if (shape == 1)
     return launch_prefill_shape<kPaged, 1>(tq, tk, tv, to, p, num_heads, batch, max_seqlen_q, stream);
+  if constexpr (!kPaged) {
+    if (shape == 3)
+      return launch_prefill_shape<false, 3>(tq, tk, tv, to, p, num_heads, batch, max_seqlen_q, stream);
+  }
   return launch_prefill_shape<kPaged, 2>(tq, tk, tv, to, p, num_heads, batch, max_seqlen_q, stream);
 }
 
@@ -847,7 +1017,7 @@ static char *mha_varlen_fwd_impl(const char *fn, void *const *outs, int world, i
                                      int64_t v_tok_stride, int64_t v_head_stride,
                                      int64_t o_tok_stride, int64_t o_head_stride,
                                      float softmax_scale, int is_causal, int dtype,
-                                     aici_stream_t stream) {
+                                     aici_stream_t stream, int forced_shape = 0) {
   void *out = outs[0];
   for (int w = 1; w < world; ++w)
     AICI_CHECK(outs[w] != nullptr && (uintptr_t)outs[w] % 16 == 0,
@@ -885,7 +1055,10 @@ static char *mha_varlen_fwd_impl(const char *fn, void *const *outs, int world, i
   const void *kk = total_k > 0 ? k : q;
   const void *vv = total_k > 0 ? v : q;
   const int64_t tk_rows = total_k > 0 ? total_k : 1;
-  if (char *e = make_tmap(fn, &tk, kk, tk_rows, num_heads_k, k_tok_stride, k_head_stride)) return e;
+  int shape = 0;
+  if (char *e = pick_shape(fn, forced_shape, false, num_heads, num_heads / num_heads_k, max_seqlen_k, &shape)) return e;
+  // the CTA-pair shape loads key tiles in halves of 64 tokens
+  if (char *e = make_tmap(fn, &tk, kk, tk_rows, num_heads_k, k_tok_stride, k_head_stride, shape == 3 ? 64 : kBM)) return e;
   if (char *e = make_tmap(fn, &tv, vv, tk_rows, num_heads_k, v_tok_stride, v_head_stride)) return e;
 
   PrefillParams p;
@@ -911,7 +1084,7 @@ static char *mha_varlen_fwd_impl(const char *fn, void *const *outs, int world, i
   for (int w = 0; w < world; ++w)  // the kernel reads m[w] for w < world only
     if (char *e = make_tmap(fn, &to.m[w], outs[w], total_q, out_head0 + num_heads, o_tok_stride, o_head_stride))
       return e;
-  return launch_prefill<false>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q, max_seqlen_k,
+  return launch_prefill<false>(shape, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q,
                                static_cast<cudaStream_t>(stream));
 }
 
@@ -931,6 +1104,27 @@ extern "C" char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, co
                              max_seqlen_k, q_tok_stride, q_head_stride, k_tok_stride, k_head_stride,
                              v_tok_stride, v_head_stride, o_tok_stride, o_head_stride, softmax_scale,
                              is_causal, dtype, stream);
+}
+
+// aici_mha_varlen_fwd with the kernel shape chosen by the caller instead of by sequence length (test
+// and benchmark hook): 0 = automatic, 1 = one query tile per CTA and two CTAs per SM, 2 = two query
+// tiles per CTA, 3 = shape 2 on CTA pairs with two-SM MMAs (tcgen05 cta_group::2).
+extern "C" char *aici_mha_varlen_fwd_shape(void *out, const void *q, const void *k, const void *v,
+                                           const int32_t *cu_seqlens_q, const int32_t *cu_seqlens_k,
+                                           int batch, int total_q, int total_k, int num_heads,
+                                           int num_heads_k, int head_size, int max_seqlen_q,
+                                           int max_seqlen_k, int64_t q_tok_stride, int64_t q_head_stride,
+                                           int64_t k_tok_stride, int64_t k_head_stride,
+                                           int64_t v_tok_stride, int64_t v_head_stride,
+                                           int64_t o_tok_stride, int64_t o_head_stride,
+                                           float softmax_scale, int is_causal, int shape, int dtype,
+                                           aici_stream_t stream) {
+  void *outs[1] = {out};
+  return mha_varlen_fwd_impl("aici_mha_varlen_fwd_shape", outs, 1, 0, q, k, v, cu_seqlens_q, cu_seqlens_k,
+                             batch, total_q, total_k, num_heads, num_heads_k, head_size, max_seqlen_q,
+                             max_seqlen_k, q_tok_stride, q_head_stride, k_tok_stride, k_head_stride,
+                             v_tok_stride, v_head_stride, o_tok_stride, o_head_stride, softmax_scale,
+                             is_causal, dtype, stream, shape);
 }
 
 // Prefill attention whose epilogue is the head-output gather: each finished output tile is stored
@@ -1022,6 +1216,8 @@ extern "C" char *aici_mha_varlen_paged_fwd(void *out, const void *q, const void 
   p.total_q = total_q;
   p.tma_store = 1;
   if (char *e = make_tmap(fn, &to.m[0], out, total_q, num_heads, o_tok_stride, o_head_stride)) return e;
-  return launch_prefill<true>(fn, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q, max_context_len,
+  int shape = 0;
+  if (char *e = pick_shape(fn, 0, true, num_heads, num_heads / num_kv_heads, max_context_len, &shape)) return e;
+  return launch_prefill<true>(shape, tq, tk, tv, to, p, num_heads, batch, max_seqlen_q,
                               static_cast<cudaStream_t>(stream));
 }

@@ -83,10 +83,11 @@ def _cache_dims(fn: str, key_cache: torch.Tensor, value_cache: torch.Tensor):
 
 def flash_attn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seqlens_q: torch.Tensor,
                       seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int,
-                      softmax_scale: float, causal: bool) -> torch.Tensor:
+                      softmax_scale: float, causal: bool, shape: int = 0) -> torch.Tensor:
     """softmax(Q K^T * softmax_scale) V over packed variable-length sequences; returns a new
     tensor [total_q, num_heads_q, head_size] (lib.rs:49-104).  `seqlens_*` are the cumulative
-    lengths, int32, batch + 1 entries."""
+    lengths, int32, batch + 1 entries.  `shape` (not in the crate; tests and benchmarks) forces one
+    of the kernel's shapes, see aici_mha_varlen_fwd_shape; 0 lets the sequence length choose."""
     fn = "flash_attn_varlen"
     dev = _require_cuda(fn, q, k, v, seqlens_q, seqlens_k)
     if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
@@ -114,9 +115,7 @@ def flash_attn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seqlens
     if tuple(v.shape) != tuple(k.shape) or k.shape[2] != head_size:
         raise AiciError("%s: k and v must be [total_k, num_heads_k, head_size]" % fn)
     out = torch.empty((total_q, num_heads, head_size), dtype=q.dtype, device=dev)
-    with _on_device(dev):
-        res = _lib.lib().aici_mha_varlen_fwd(
-            _p(out), _p(q), _p(k), _p(v), _p(seqlens_q), _p(seqlens_k), ctypes.c_int(batch),
+    head = (_p(out), _p(q), _p(k), _p(v), _p(seqlens_q), _p(seqlens_k), ctypes.c_int(batch),
             ctypes.c_int(total_q), ctypes.c_int(total_k), ctypes.c_int(num_heads),
             ctypes.c_int(num_heads_k), ctypes.c_int(head_size), ctypes.c_int(int(max_seqlen_q)),
             ctypes.c_int(int(max_seqlen_k)),
@@ -124,8 +123,13 @@ def flash_attn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seqlens
             ctypes.c_int64(k.stride(0)), ctypes.c_int64(k.stride(1)),
             ctypes.c_int64(v.stride(0)), ctypes.c_int64(v.stride(1)),
             ctypes.c_int64(out.stride(0)), ctypes.c_int64(out.stride(1)),
-            ctypes.c_float(softmax_scale), ctypes.c_int(1 if causal else 0),
-            ctypes.c_int(_dtype(fn, q)), _stream(dev))
+            ctypes.c_float(softmax_scale), ctypes.c_int(1 if causal else 0))
+    with _on_device(dev):
+        if shape:
+            res = _lib.lib().aici_mha_varlen_fwd_shape(*head, ctypes.c_int(int(shape)), ctypes.c_int(_dtype(fn, q)),
+                                                       _stream(dev))
+        else:
+            res = _lib.lib().aici_mha_varlen_fwd(*head, ctypes.c_int(_dtype(fn, q)), _stream(dev))
     _lib.check(fn, res)
     return out
 

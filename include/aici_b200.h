@@ -208,6 +208,20 @@ char *aici_mha_varlen_fwd(void *out, const void *q, const void *k, const void *v
                           int64_t o_tok_stride, int64_t o_head_stride, float softmax_scale,
                           int is_causal, int dtype, aici_stream_t stream);
 
+/* Test and benchmark hook (no counterpart in the reference): aici_mha_varlen_fwd with the kernel
+ * shape given by the caller instead of chosen by sequence length.  shape 0 = automatic (what
+ * aici_mha_varlen_fwd does: 1 up to 1024 keys, 2 above), 1 = one query tile per CTA, two CTAs per
+ * SM, 2 = two query tiles per CTA sharing their key/value tiles, 3 = shape 2 on pairs of CTAs whose
+ * MMAs span two SMs (tcgen05 cta_group::2; needs num_heads / num_heads_k to be a multiple of 4). */
+char *aici_mha_varlen_fwd_shape(void *out, const void *q, const void *k, const void *v,
+                                const int32_t *cu_seqlens_q, const int32_t *cu_seqlens_k, int batch,
+                                int total_q, int total_k, int num_heads, int num_heads_k, int head_size,
+                                int max_seqlen_q, int max_seqlen_k, int64_t q_tok_stride,
+                                int64_t q_head_stride, int64_t k_tok_stride, int64_t k_head_stride,
+                                int64_t v_tok_stride, int64_t v_head_stride, int64_t o_tok_stride,
+                                int64_t o_head_stride, float softmax_scale, int is_causal, int shape,
+                                int dtype, aici_stream_t stream);
+
 /* ---- multi-GPU: attention whose epilogue is the head-output gather -------------------------
  * The reference has no multi-GPU code; its only hook is the per-rank kv-head count
  * (rllm-cuda/src/llm/config.rs:49-51).  With kv heads sharded over the GPUs of one box every rank
