@@ -142,9 +142,9 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   constexpr uint32_t kOCol = 128u * kTiles;  // first column of O0
   extern __shared__ uint8_t smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // shape 1 orders its grid (head, sequence, row tile) so that the row tile is the slowest index: all
-  // the longest tiles of the batch start first and the one-key-tile CTAs fill the tail
-  const int b = kTiles == 1 ? blockIdx.y : blockIdx.z;
+  // The grid is ordered (head, sequence, row tile) with the row tile as the slowest index: all the
+  // longest tiles of the batch start first and the CTAs with one key tile fill the tail.
+  const int b = blockIdx.y;
   const int q0 = p.cu_q[b], lq = p.cu_q[b + 1] - q0;
   int k0 = 0, lk = 0;
   if (kPaged) {
@@ -169,18 +169,18 @@ varlen_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       mb[1] = -1;  // no second tile
       hh[0] = hh[1] = (int)blockIdx.x;
     } else if (kPair) {
-      // clusters of two CTAs along x: CTA x = 2m + r holds heads 4y + 2r and 4y + 2r + 1 of row tile m
-      mb[0] = mb[1] = n_mblocks - 1 - (int)(blockIdx.x >> 1);
-      hh[0] = 4 * (int)blockIdx.y + 2 * (int)(blockIdx.x & 1);
+      // clusters of two CTAs along x: CTA x = 2y + r holds heads 4y + 2r and 4y + 2r + 1
+      mb[0] = mb[1] = n_mblocks - 1 - (int)blockIdx.z;
+      hh[0] = 2 * (int)blockIdx.x;
       hh[1] = hh[0] + 1;
     } else if (p.pair_heads) {
-      mb[0] = mb[1] = n_mblocks - 1 - (int)blockIdx.x;
-      hh[0] = 2 * (int)blockIdx.y;
+      mb[0] = mb[1] = n_mblocks - 1 - (int)blockIdx.z;
+      hh[0] = 2 * (int)blockIdx.x;
       hh[1] = hh[0] + 1;
     } else {
-      mb[1] = n_mblocks - 1 - 2 * (int)blockIdx.x;
+      mb[1] = n_mblocks - 1 - 2 * (int)blockIdx.z;
       mb[0] = mb[1] - 1;
-      hh[0] = hh[1] = (int)blockIdx.y;
+      hh[0] = hh[1] = (int)blockIdx.x;
     }
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
@@ -911,7 +911,7 @@ static char *make_cache_tmap(const char *fn, CUtensorMap *map, const void *base,
 // as three key tiles) is what two resident CTAs hide; with many, sharing each K/V tile between two
 // query tiles (half the shared-memory traffic) is worth more.
 #ifndef AICI_PREFILL_ONE_TILE_MAX_K
-#define AICI_PREFILL_ONE_TILE_MAX_K 1024
+#define AICI_PREFILL_ONE_TILE_MAX_K 2048
 #endif
 
 template <bool kPaged, int kShape>
@@ -930,14 +930,13 @@ static char *launch_prefill_shape(const CUtensorMap &tq, const CUtensorMap &tk, 
   dim3 grid;
   if (Cfg::kTiles == 1) {
     grid = dim3(num_heads, batch, mblocks);
-  } else if (Cfg::kPair) {
-    p.pair_heads = 1;
-    grid = dim3(2 * mblocks, num_heads / 4, batch);
   } else {
-    // two tiles per CTA: two heads of one kv group when the group is even, else two row tiles
-    p.pair_heads = (p.group % 2 == 0) ? 1 : 0;
-    grid = dim3(p.pair_heads ? mblocks : (mblocks + 1) / 2, p.pair_heads ? num_heads / 2 : num_heads, batch);
+    // two tiles per CTA: two heads of one kv group when the group is even (always so for CTA pairs,
+    // whose two CTAs are neighbours in x: four heads of one kv head), else two row tiles
+    p.pair_heads = (Cfg::kPair || p.group % 2 == 0) ? 1 : 0;
+    grid = dim3(p.pair_heads ? num_heads / 2 : num_heads, batch, p.pair_heads ? mblocks : (mblocks + 1) / 2);
   }
+  AICI_CHECK(grid.y <= 65535 && grid.z <= 65535, "prefill: batch and row tiles must fit a grid dimension");
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(Cfg::kThreads);
@@ -1045,6 +1044,8 @@ static char *mha_varlen_fwd_impl(const char *fn, void *const *outs, int world, i
                  (int64_t)(out_head0 + num_heads - 1) * o_head_stride + kHD <= o_tok_stride,
              "%s: heads [%d, %d) do not fit an output row of %lld elements", fn, out_head0,
              out_head0 + num_heads, (long long)o_tok_stride);
+  int shape = 0;
+  if (char *e = pick_shape(fn, forced_shape, false, num_heads, num_heads / num_heads_k, max_seqlen_k, &shape)) return e;
   if (char *e = check_on_current_device(fn, "q", q)) return e;
   unsigned int *st = status_ptr();
   AICI_CHECK(st != nullptr, "%s: no CUDA device", fn);
@@ -1055,8 +1056,6 @@ static char *mha_varlen_fwd_impl(const char *fn, void *const *outs, int world, i
   const void *kk = total_k > 0 ? k : q;
   const void *vv = total_k > 0 ? v : q;
   const int64_t tk_rows = total_k > 0 ? total_k : 1;
-  int shape = 0;
-  if (char *e = pick_shape(fn, forced_shape, false, num_heads, num_heads / num_heads_k, max_seqlen_k, &shape)) return e;
   // the CTA-pair shape loads key tiles in halves of 64 tokens
   if (char *e = make_tmap(fn, &tk, kk, tk_rows, num_heads_k, k_tok_stride, k_head_stride, shape == 3 ? 64 : kBM)) return e;
   if (char *e = make_tmap(fn, &tv, vv, tk_rows, num_heads_k, v_tok_stride, v_head_stride)) return e;

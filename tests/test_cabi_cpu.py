@@ -70,6 +70,41 @@ def test_version_and_error_convention(built_lib):
     assert 64 * 32 * 130 * 4 < need < (64 * 32 + 4 * 2 * 256) * 132 * 4
 
 
+def test_argument_checks_of_the_multi_gpu_entry_points(built_lib):
+    """Host-side validation only (pointers are never dereferenced before these checks fail)."""
+    lib = _lib.lib()
+    fake = ctypes.c_void_p(0x10000)
+    outs = (ctypes.c_void_p * 2)(fake, fake)
+    i64 = ctypes.c_int64
+    # this rank's heads [6, 10) do not fit an 8-head output row
+    res = lib.aici_mha_varlen_fwd_peers(outs, 2, 6, fake, fake, fake, fake, fake, 1, 128, 128, 4, 4, 128, 128, 128,
+                                        i64(512), i64(128), i64(512), i64(128), i64(512), i64(128), i64(1024),
+                                        i64(128), ctypes.c_float(0.1), 1, 0, None)
+    with pytest.raises(AiciError, match="do not fit an output row"):
+        _lib.check("flash_attn_varlen_peers", res)
+    res = lib.aici_paged_attention_v1_peers_barrier(outs, outs, 2, 2, 8, 0, *[None] * 3, 4, ctypes.c_float(1.0),
+                                                    None, None, 16, 64, 1, 4, 128, 4, i64(8), i64(512), i64(1),
+                                                    i64(1), None, ctypes.c_size_t(0), 0, None)
+    with pytest.raises(AiciError, match="rank inside it"):
+        _lib.check("paged_attention_v1_peers_barrier", res)
+    res = lib.aici_gather_heads(outs, 2, 8, 6, fake, i64(4), 4, 128, i64(512), 0, None)
+    with pytest.raises(AiciError, match="do not fit 8 total heads"):
+        _lib.check("gather_heads", res)
+    res = lib.aici_peer_open(None, None)
+    with pytest.raises(AiciError, match="NULL pointer"):
+        _lib.check("peer_open", res)
+    bogus = (ctypes.c_ubyte * 128)()
+    out = ctypes.c_void_p(0)
+    res = lib.aici_peer_open(bogus, ctypes.byref(out))
+    with pytest.raises(AiciError, match="not a handle made by aici_peer_alloc"):
+        _lib.check("peer_open", res)
+    res = lib.aici_mha_varlen_fwd_shape(fake, fake, fake, fake, fake, fake, 1, 128, 128, 4, 4, 128, 128, 128,
+                                        *[i64(512), i64(128)] * 4, ctypes.c_float(0.1), 1, 3, 0, None)
+    with pytest.raises(AiciError, match="multiple of 4"):
+        _lib.check("flash_attn_varlen", res)
+    assert lib.aici_paged_attention_chunked_workspace_bytes(64, 32, 32, 4096, 24) == 256  # invalid chunk size
+
+
 def test_product_path_refuses_cpu_tensors():
     k = torch.zeros(1, 2, 128, dtype=torch.bfloat16)
     kc = torch.zeros(2, 2, 16, 16, 8, dtype=torch.bfloat16)
