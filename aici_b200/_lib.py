@@ -32,6 +32,7 @@ EXPORTS = (
     "aici_mha_varlen_fwd_peers",
     "aici_peer_barrier",
     "aici_paged_attention_v1_peers_barrier",
+    "aici_decode_step",
     "aici_peer_alloc",
     "aici_peer_open",
     "aici_peer_close",

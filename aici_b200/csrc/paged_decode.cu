@@ -69,6 +69,14 @@ struct DecodeParams {
   // fused cross-GPU barrier in the merge kernel's tail (sync != 0): rank p's flag array
   unsigned int *peer_flags[8];
   int sync, rank;
+  // decode step (aici_decode_step): the step's new tokens, one per sequence, still outside the cache.
+  // The warp that works on the last tile of a (sequence, kv head) row -- there is exactly one --
+  // puts the token into the tile it has staged in shared memory and writes it to the cache.
+  const __nv_bfloat16 *new_k;  // [num_seqs, num_kv_heads, 128], NULL = plain decode
+  const __nv_bfloat16 *new_v;
+  const void *new_slots;       // [num_seqs] int32 or int64; must name position context_len - 1
+  int new_slot_is_int64;
+  int64_t new_k_stride, new_v_stride;
 };
 
 struct Item {
@@ -352,6 +360,48 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
       const uint32_t kbase = smem_u32(ring + stage * kStageBytes);
       const uint32_t vbase = kbase + kTileBytes;
 
+      if (p.new_k != nullptr && it.tok0 + (t + 1) * kB >= it.ctx) {
+        // The tile that ends the row holds position ctx - 1, the token of this step, which is not
+        // in the cache yet: take it from the step's inputs, put it into the staged tile, and write it
+        // to the cache (what reshape_and_cache would have done before this kernel).  No other warp
+        // reads this tile, and this warp's own copy of it has landed, so nothing races.
+        const int pos = it.ctx - 1 - (it.tok0 + t * kB);
+        const int64_t slot = p.new_slot_is_int64 ? static_cast<const int64_t *>(p.new_slots)[it.seq]
+                                                  : (int64_t) static_cast<const int32_t *>(p.new_slots)[it.seq];
+        int blk = p.block_tables[(int64_t)it.seq * p.max_blocks_per_seq + (it.ctx - 1) / kB];
+        if (blk < 0 || blk >= p.num_blocks) blk = 0;  // recorded by the producer when it fetched the id
+        if (slot == (int64_t)blk * kB + pos) {
+          uint8_t *ktile = ring + stage * kStageBytes;
+          uint8_t *vtile = ktile + kTileBytes;
+          const int64_t coff = (int64_t)blk * p.kv_block_stride + (int64_t)it.kvh * p.kv_head_stride;
+          // (Measured: writing whole 32-byte sectors or whole lines of the patched tile back instead
+          // of these 2-byte pieces is not faster.  What the write costs -- about 13 us at 64 sequences
+          // x 32 heads, wherever it is issued from -- is the later write-back of its 98 000 dirty
+          // lines, one read/write turn-around of a memory channel each, in the middle of the key/value
+          // stream; the reference's value layout [d][token] puts one token into every sector of a tile.)
+          if (lane < kD / 8) {  // key: chunk `lane` (8 elements) -> [chunk][pos][0..7]
+            const uint4 kv = *reinterpret_cast<const uint4 *>(p.new_k + (int64_t)it.seq * p.new_k_stride +
+                                                              it.kvh * kD + lane * 8);
+            *reinterpret_cast<uint4 *>(ktile + (lane * kB + pos) * 16) = kv;
+            *reinterpret_cast<uint4 *>(const_cast<__nv_bfloat16 *>(p.k_cache) + coff + (lane * kB + pos) * 8) = kv;
+          }
+          const uint2 raw = *reinterpret_cast<const uint2 *>(p.new_v + (int64_t)it.seq * p.new_v_stride +
+                                                             it.kvh * kD + lane * 4);
+          const uint16_t e[4] = {(uint16_t)(raw.x & 0xffffu), (uint16_t)(raw.x >> 16), (uint16_t)(raw.y & 0xffffu),
+                                 (uint16_t)(raw.y >> 16)};
+          uint16_t *vg = reinterpret_cast<uint16_t *>(const_cast<__nv_bfloat16 *>(p.v_cache) + coff);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {  // value: element d = 4 lane + j -> [d][pos]
+            const int d = lane * 4 + j;
+            *reinterpret_cast<uint16_t *>(vtile + d * (kB * 2) + pos * 2) = e[j];
+            vg[d * kB + pos] = e[j];
+          }
+        } else if (slot >= 0 && lane == 0) {
+          set_status(p.status, AICI_STATUS_BAD_SLOT);  // not the sequence's last position: not written
+        }
+        __syncwarp();
+      }
+
       // ---- S = Q K^T (16 x 16) -------------------------------------------------------
       float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -456,6 +506,9 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
 constexpr int kMergeWarps = 8;
 template <typename PartT, bool kSpans, int kTeam>
 __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const DecodeParams p) {
+  // a grid launched as a programmatic dependent of this one (the next step's cache write, the next
+  // decode call) may become resident now; it waits for this grid before it touches anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");  // no-op unless launched as a dependent grid
   constexpr int kRows = kMergeWarps / kTeam;
   __shared__ float s_acc[kMergeWarps][kD];
@@ -720,6 +773,15 @@ static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaS
   if (char *e = once.run([&]() -> char * {
         AICI_CUDA(cudaFuncSetAttribute(paged_decode_kernel<PartT, kSpans>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        // An SM changes its shared-memory / L1 split only when it is empty.  The merge kernel needs
+        // 4 KB of shared memory and would get a small carve-out by default, so its CTAs could not
+        // join an SM that still runs decode CTAs (or the other way round at the next call) and the
+        // programmatic launch would overlap nothing.  Asking for the largest carve-out keeps every
+        // kernel of a decode step on one SM configuration.
+        AICI_CUDA(cudaFuncSetAttribute(paged_merge_kernel<PartT, kSpans, 1>,
+                                       cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        AICI_CUDA(cudaFuncSetAttribute(paged_merge_kernel<PartT, kSpans, kMergeWarps>,
+                                       cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         return nullptr;
       }))
     return e;
@@ -801,6 +863,13 @@ extern "C" size_t aici_paged_attention_chunked_workspace_bytes(int num_seqs, int
 
 // forced_chunk < 0: the default traversal; 0: the fixed-chunk traversal with its own chunk size;
 // > 0: the fixed-chunk traversal with that many tokens per chunk.
+// The new tokens of a decode step (aici_decode_step).
+struct StepTokens {
+  const void *key, *value, *slots;
+  int slot_is_int64;
+  int64_t key_stride, value_stride;
+};
+
 static char *paged_attention_v1_impl(const char *fn, void *const *outs, int world, int out_heads,
                                      int out_head0, const void *query, const void *key_cache,
                                      const void *value_cache, int num_kv_heads, float scale,
@@ -811,7 +880,7 @@ static char *paged_attention_v1_impl(const char *fn, void *const *outs, int worl
                                      int64_t kv_block_stride, int64_t kv_head_stride, void *workspace,
                                      size_t workspace_bytes, int dtype, aici_stream_t stream,
                                      int forced_chunk = -1, void *const *peer_flags = nullptr,
-                                     int rank = 0) {
+                                     int rank = 0, const StepTokens *step = nullptr) {
   void *out = outs[0];
   for (int w = 1; w < world; ++w)
     AICI_CHECK(outs[w] != nullptr && (uintptr_t)outs[w] % 16 == 0,
@@ -868,6 +937,12 @@ static char *paged_attention_v1_impl(const char *fn, void *const *outs, int worl
   p.status = st;
   p.sync = peer_flags != nullptr && world > 1 ? 1 : 0;
   p.rank = rank;
+  p.new_k = static_cast<const __nv_bfloat16 *>(step ? step->key : nullptr);
+  p.new_v = static_cast<const __nv_bfloat16 *>(step ? step->value : nullptr);
+  p.new_slots = step ? step->slots : nullptr;
+  p.new_slot_is_int64 = step ? step->slot_is_int64 : 0;
+  p.new_k_stride = step ? step->key_stride : 0;
+  p.new_v_stride = step ? step->value_stride : 0;
   for (int i = 0; i < 8; ++i)
     p.peer_flags[i] = static_cast<unsigned int *>(p.sync && i < world ? peer_flags[i] : nullptr);
   if (spans) return launch_decode<float, true>(p, nullptr, nullptr, static_cast<cudaStream_t>(stream));
@@ -950,6 +1025,53 @@ extern "C" char *aici_paged_attention_v1_peers_barrier(
   return nullptr;
 }
 
+// One decode step of one layer in one call: the cache write of the step's new tokens
+// (reshape_and_cache: token i is the newest token of sequence i) and decode attention over the
+// cache, which rLLM issues as two kernels back to back (rllm-cuda/src/llm/mod.rs:132-166 then
+// :280-316).  Here the cache write has no launch of its own: the warp of the decode kernel that
+// works on the last tile of a (sequence, kv head) row takes the new token from the call's inputs,
+// places it in the tile it has staged and writes it to the cache.  With world > 1 the call is also
+// the head-output gather (outs / flag_ptrs as in aici_paged_attention_v1_peers_barrier); with
+// world == 1, outs[0] is the output and flag_ptrs may be NULL.
+extern "C" char *aici_decode_step(void *const *outs, void *const *flag_ptrs, int world, int rank,
+                                  int total_heads, int head0, const void *new_key, const void *new_value,
+                                  const void *slot_mapping, int slot_is_int64, int64_t key_stride,
+                                  int64_t value_stride, const void *query, void *key_cache,
+                                  void *value_cache, int num_kv_heads, float scale,
+                                  const int32_t *block_tables, const int32_t *context_lens, int block_size,
+                                  int max_context_len, int num_seqs, int num_heads, int head_size,
+                                  int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_stride,
+                                  int64_t kv_block_stride, int64_t kv_head_stride, void *workspace,
+                                  size_t workspace_bytes, int dtype, aici_stream_t stream) {
+  const char *fn = "aici_decode_step";
+  AICI_CHECK(outs != nullptr && world >= 1 && world <= 8 && rank >= 0 && rank < world,
+             "%s: world must be 1..8 and rank inside it", fn);
+  AICI_CHECK(world == 1 || flag_ptrs != nullptr, "%s: flag arrays are needed with more than one rank", fn);
+  AICI_CHECK(head0 >= 0 && num_heads > 0 && head0 + num_heads <= total_heads,
+             "%s: heads [%d, %d) do not fit %d total heads", fn, head0, head0 + num_heads, total_heads);
+  for (int i = 0; world > 1 && i < world; ++i)
+    AICI_CHECK(flag_ptrs[i] != nullptr && (uintptr_t)flag_ptrs[i] % 4 == 0,
+               "%s: flag array %d must be non-NULL and 4-byte aligned", fn, i);
+  if (num_seqs > 0) {
+    AICI_CHECK(new_key && new_value && slot_mapping, "%s: NULL pointer", fn);
+    AICI_CHECK(((uintptr_t)new_key | (uintptr_t)new_value) % 16 == 0, "%s: tensors must be 16-byte aligned", fn);
+    AICI_CHECK(num_kv_heads > 0 && key_stride % 8 == 0 && value_stride % 8 == 0 &&
+                   key_stride >= (int64_t)num_kv_heads * 128 && value_stride >= (int64_t)num_kv_heads * 128,
+               "%s: token strides must be multiples of 8 elements and cover one row", fn);
+    AICI_CHECK(num_seqs <= kMaxInlineSeqs, "%s: at most %d sequences per call", fn, kMaxInlineSeqs);
+  }
+  const StepTokens step = {new_key, new_value, slot_mapping, slot_is_int64, key_stride, value_stride};
+  if (char *e = paged_attention_v1_impl(fn, outs, world, total_heads, head0, query, key_cache, value_cache,
+                                        num_kv_heads, scale, block_tables, context_lens, block_size,
+                                        max_context_len, nullptr, num_seqs, num_heads, head_size,
+                                        max_num_blocks_per_seq, num_blocks, q_stride, kv_block_stride,
+                                        kv_head_stride, workspace, workspace_bytes, dtype, stream, -1,
+                                        world > 1 ? flag_ptrs : nullptr, rank, &step))
+    return e;
+  if (num_seqs == 0 && world > 1) return aici_peer_barrier(flag_ptrs, world, rank, stream);
+  return nullptr;
+}
+
 // aici_paged_attention_v1 through the fixed-chunk traversal (every sequence cut into chunks of
 // chunk_tokens tokens, dealt out round-robin): kept so that tests and benchmarks can compare the two
 // traversals.  The chunk size is an argument of the call; nothing process-wide is changed.
@@ -1024,6 +1146,10 @@ extern "C" char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_
   p.status = st;
   p.sync = 0;
   p.rank = 0;
+  p.new_k = p.new_v = nullptr;
+  p.new_slots = nullptr;
+  p.new_slot_is_int64 = 0;
+  p.new_k_stride = p.new_v_stride = 0;
   for (int i = 0; i < 8; ++i) p.peer_flags[i] = nullptr;
   return launch_decode<__nv_bfloat16, false>(p, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }

@@ -583,6 +583,69 @@ def paged_attention_v1_peers(peer_ptrs: Sequence[int], total_heads: int, head0: 
     _lib.check(fn, res)
 
 
+def decode_step(out: Optional[torch.Tensor], new_key: torch.Tensor, new_value: torch.Tensor,
+                slot_mapping: torch.Tensor, query: torch.Tensor, key_cache: torch.Tensor,
+                value_cache: torch.Tensor, num_kv_heads: int, scale: float, block_tables: torch.Tensor,
+                context_lens: torch.Tensor, block_size: int, max_context_len: int,
+                peer_ptrs: Optional[Sequence[int]] = None, barrier_flags: Optional[Sequence[int]] = None,
+                rank: int = 0, total_heads: int = 0, head0: int = 0) -> None:
+    """reshape_and_cache(new_key, new_value, ..., slot_mapping) followed by paged_attention_v1 into
+    `out`, as one call (aici_decode_step): token i must be the newest token of sequence i
+    (slot_mapping[i] = the cache slot of position context_lens[i] - 1); the library then lets the
+    decode kernel read the rest of the cache while the write is still running.  With `peer_ptrs` /
+    `barrier_flags` the output rows go to every rank's buffer instead of `out` and the call ends with
+    the ranks' barrier (see paged_attention_v1_peers)."""
+    fn = "decode_step"
+    dev = _require_cuda(fn, new_key, new_value, slot_mapping, query, key_cache, value_cache, block_tables,
+                        context_lens)
+    num_blocks, cache_kv_heads, head_size, cache_block = _cache_dims(fn, key_cache, value_cache)
+    if cache_kv_heads != num_kv_heads or cache_block != block_size:
+        raise AiciError("%s: num_kv_heads / block_size do not match the cache" % fn)
+    if query.dim() != 3 or query.shape[2] != head_size or query.stride(2) != 1 or query.stride(1) != head_size:
+        raise AiciError("%s: query rows must hold contiguous heads of the cache's head_size" % fn)
+    num_seqs, num_heads, _ = query.shape
+    if tuple(new_key.shape) != (num_seqs, num_kv_heads, head_size) or tuple(new_value.shape) != tuple(new_key.shape):
+        raise AiciError("%s: new key/value must be [num_seqs, num_kv_heads, head_size]" % fn)
+    if new_key.stride(2) != 1 or new_key.stride(1) != head_size or new_value.stride(2) != 1 or \
+            new_value.stride(1) != head_size:
+        raise AiciError("%s: heads of one token must be contiguous" % fn)
+    if slot_mapping.dtype not in (torch.int32, torch.int64) or not slot_mapping.is_contiguous() or \
+            slot_mapping.numel() != num_seqs:
+        raise AiciError("%s: slot_mapping must be contiguous int32 or int64 with one entry per sequence" % fn)
+    if block_tables.dtype != torch.int32 or context_lens.dtype != torch.int32 or \
+            not block_tables.is_contiguous() or not context_lens.is_contiguous():
+        raise AiciError("%s: block_tables and context_lens must be contiguous int32" % fn)
+    if peer_ptrs is None:
+        if out is None or tuple(out.shape) != tuple(query.shape) or not out.is_contiguous() or out.device != dev:
+            raise AiciError("%s: out must be a contiguous tensor shaped like query" % fn)
+        ptrs, world, flags = [out.data_ptr()], 1, None
+        total_heads, head0 = num_heads, 0
+    else:
+        ptrs, world = [int(x) for x in peer_ptrs], len(peer_ptrs)
+        if world > 1 and (barrier_flags is None or len(barrier_flags) != world):
+            raise AiciError("%s: one flag array per rank is needed" % fn)
+        flags = barrier_flags
+    outs = (ctypes.c_void_p * world)(*[ctypes.c_void_p(x) for x in ptrs])
+    flag_arr = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in flags]) if flags is not None else None
+    L = _lib.lib()
+    with _on_device(dev):
+        nbytes = L.aici_paged_attention_workspace_bytes(
+            ctypes.c_int(num_seqs), ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads),
+            ctypes.c_int(int(max_context_len)))
+        ws = _workspace(dev, nbytes)
+        res = L.aici_decode_step(
+            outs, flag_arr, ctypes.c_int(world), ctypes.c_int(rank), ctypes.c_int(total_heads), ctypes.c_int(head0),
+            _p(new_key), _p(new_value), _p(slot_mapping), ctypes.c_int(1 if slot_mapping.dtype == torch.int64 else 0),
+            ctypes.c_int64(new_key.stride(0)), ctypes.c_int64(new_value.stride(0)), _p(query), _p(key_cache),
+            _p(value_cache), ctypes.c_int(num_kv_heads), ctypes.c_float(scale), _p(block_tables), _p(context_lens),
+            ctypes.c_int(block_size), ctypes.c_int(int(max_context_len)), ctypes.c_int(num_seqs),
+            ctypes.c_int(num_heads), ctypes.c_int(head_size), ctypes.c_int(block_tables.shape[1]),
+            ctypes.c_int64(num_blocks), ctypes.c_int64(query.stride(0)), ctypes.c_int64(key_cache.stride(0)),
+            ctypes.c_int64(key_cache.stride(1)), _p(ws), ctypes.c_size_t(ws.numel()),
+            ctypes.c_int(_dtype(fn, query)), _stream(dev))
+    _lib.check(fn, res)
+
+
 def gather_heads(peer_ptrs: Sequence[int], total_heads: int, head0: int, local: torch.Tensor) -> None:
     """Stores local [rows, heads, 128] at head index head0 + h of every rank's
     [rows, total_heads, 128] buffer in `peer_ptrs` (the head-output gather as a call of its own; a

@@ -439,10 +439,28 @@ def run_ours(args):
             return gathered
         return out
 
+    def full_step(nk, nv, slots, q, bt, cl, pool, buf):
+        """One decode step: cache write of the new tokens + decode attention + head gather.  By default
+        one library call (aici_decode_step: same two kernels, the decode grid streams everything but the
+        sequences' last tiles while the cache write runs); --separate-calls makes the two crate calls."""
+        kc, vc = pools[pool]
+        if args.separate_calls:
+            tch_cuda.reshape_and_cache(nk, nv, kc, vc, slots)
+            return attention(q, bt, cl, pool, buf)
+        if fused:
+            tch_cuda.decode_step(None, nk, nv, slots, q, kc, vc, w.num_kv_heads, w.scale, bt, cl, 16,
+                                 w.max_context_len, peer_ptrs=pg._ptrs[buf], barrier_flags=pg.flag_ptrs,
+                                 rank=pg.rank, total_heads=hq_total, head0=pg.head0)
+            return pg.tensors[buf]
+        tch_cuda.decode_step(out, nk, nv, slots, q, kc, vc, w.num_kv_heads, w.scale, bt, cl, 16, w.max_context_len)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1, hq_local, 128), out)
+            return gathered
+        return out
+
     def step(i=0):
-        kc, vc = pools[i % n_pools]
-        tch_cuda.reshape_and_cache(w.new_key, w.new_value, kc, vc, w.slot_mapping)
-        return attention(w.query, w.block_tables, w.context_lens, i % n_pools, i % 2)
+        return full_step(w.new_key, w.new_value, w.slot_mapping, w.query, w.block_tables, w.context_lens,
+                         i % n_pools, i % 2)
 
     # a graph per (pool, output buffer) combination; step i replays graph i mod n_graphs
     n_graphs = max(n_pools, 2 if fused else 1)
@@ -531,10 +549,8 @@ def run_ours(args):
     d2h = host_out.numel() * host_out.element_size()
 
     def e2e_step(i=0):
-        kc, vc = pools[i % n_pools]
         dev_in.copy_(staging, non_blocking=True)
-        tch_cuda.reshape_and_cache(d["nk"], d["nv"], kc, vc, d["slots"])
-        o = attention(d["q"], d["bt"], d["cl"], i % n_pools, i % 2)
+        o = full_step(d["nk"], d["nv"], d["slots"], d["q"], d["bt"], d["cl"], i % n_pools, i % 2)
         if world > 1 and not fused:
             o = o.permute(1, 0, 2, 3).reshape(S, hq_total, 128)
         host_out.copy_(o, non_blocking=True)
@@ -806,6 +822,8 @@ def run_ours(args):
         "config": config,
         "run": {
             "launch": "one CUDA-graph replay per step" if use_graph else "eager launches",
+            "step_call": ("reshape_and_cache, then paged_attention_v1" if args.separate_calls else
+                          "aici_decode_step (cache write and decode attention in one call, overlapped)"),
             "pool_copies": n_pools,
             "bytes_streamed_per_gpu_per_step": decode_bytes_local,
             "collective": ("none" if world == 1 else
@@ -1162,6 +1180,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch the decode step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="multi-GPU head-output gather: fused into the attention epilogue (default) or NCCL")
+    ap.add_argument("--separate-calls", action="store_true",
+                    help="make the decode step as two library calls (reshape_and_cache, paged_attention_v1) "
+                         "instead of the fused aici_decode_step")
     ap.add_argument("--headline-only", action="store_true",
                     help="skip the per-configuration entries (configs 3 and 5) of the JSON line")
     ap.add_argument("--profile-step", type=int, default=None,

@@ -275,6 +275,26 @@ char *aici_paged_attention_v1_peers_barrier(void *const *outs, void *const *flag
                                             void *workspace, size_t workspace_bytes, int dtype,
                                             aici_stream_t stream);
 
+/* One decode step of one layer in one call: aici_reshape_and_cache of the step's new tokens (token i
+ * is the newest token of sequence i: key/value [num_seqs, num_kv_heads, 128], slot_mapping[i] the
+ * cache slot of position context_lens[i] - 1) followed by aici_paged_attention_v1 -- the two crate
+ * calls rLLM makes back to back per layer (rllm-cuda/src/llm/mod.rs:132-166, 280-316).  The cache
+ * write has no launch of its own here: the warp of the decode kernel that reaches the last tile of a
+ * (sequence, kv head) row takes the new token from new_key / new_value, uses it, and writes it to
+ * the cache.  A slot that is not the sequence's last position is recorded as AICI_STATUS_BAD_SLOT
+ * and not written; a negative slot means "no new token" as in aici_reshape_and_cache.  At most 2048
+ * sequences.  world == 1: outs[0] is the output [num_seqs, num_heads, 128], flag_ptrs may be NULL,
+ * total_heads = num_heads, head0 = 0.  world > 1: as aici_paged_attention_v1_peers_barrier. */
+char *aici_decode_step(void *const *outs, void *const *flag_ptrs, int world, int rank, int total_heads,
+                       int head0, const void *new_key, const void *new_value, const void *slot_mapping,
+                       int slot_is_int64, int64_t key_stride, int64_t value_stride, const void *query,
+                       void *key_cache, void *value_cache, int num_kv_heads, float scale,
+                       const int32_t *block_tables, const int32_t *context_lens, int block_size,
+                       int max_context_len, int num_seqs, int num_heads, int head_size,
+                       int max_num_blocks_per_seq, int64_t num_blocks, int64_t q_stride,
+                       int64_t kv_block_stride, int64_t kv_head_stride, void *workspace,
+                       size_t workspace_bytes, int dtype, aici_stream_t stream);
+
 /* Peer-mapped device memory without libtorch or NCCL (no counterpart in the reference, which is
  * single-GPU; the hook this serves is the per-rank kv-head count of
  * rllm-cuda/src/llm/config.rs:30-36, 49-51).  One process per GPU:

@@ -39,6 +39,7 @@ def _worker(rank, world, port, q):
         def decode_case(name, **kw):
             shard = sharding.current_shard(kw["num_heads"], kw["num_kv_heads"])
             w = workloads.make_decode(name, dev, shard=shard, **kw)
+            kc0, vc0 = w.key_cache.clone(), w.value_cache.clone()  # the cache before this step's tokens
             tch_cuda.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping)
             # three consecutive steps with different queries: NCCL gather as the comparison ...
             queries = [w.query, (w.query * 2).contiguous(), (w.query * 0.5).contiguous()]
@@ -75,6 +76,16 @@ def _worker(rank, world, port, q):
             pg.barrier()
             torch.cuda.synchronize()
             assert torch.equal(pg.tensor.view(torch.int16), fulls[0].view(torch.int16)), name + " gather_heads"
+            # the whole step as one call: cache write inside the decode kernel, gather, barrier
+            pg.flip()
+            tch_cuda.decode_step(None, w.new_key, w.new_value, w.slot_mapping, w.query, kc0, vc0, w.num_kv_heads,
+                                 w.scale, w.block_tables, w.context_lens, 16, w.max_context_len, peer_ptrs=pg.ptrs,
+                                 barrier_flags=pg.flag_ptrs, rank=pg.rank, total_heads=kw["num_heads"],
+                                 head0=pg.head0)
+            torch.cuda.synchronize()
+            assert torch.equal(pg.tensor.view(torch.int16), fulls[0].view(torch.int16)), name + " decode_step"
+            assert torch.equal(kc0.view(torch.int16), w.key_cache.view(torch.int16)), name + " decode_step key cache"
+            assert torch.equal(vc0.view(torch.int16), w.value_cache.view(torch.int16)), name + " decode_step value cache"
             pg.close()
             full = fulls[0]
             if rank == 0:

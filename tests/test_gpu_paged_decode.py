@@ -209,3 +209,54 @@ def test_benchmark_configs_full_size(cuda_device, name):
     want = O.paged_attention_v1(w.query.cpu(), kc, vc, w.num_kv_heads, w.scale, w.block_tables.cpu(),
                                 w.context_lens.cpu())
     _check(out.cpu(), want)
+
+
+@pytest.mark.parametrize("hq,hkv,num_seqs,hi", [(32, 32, 64, 4096), (32, 8, 40, 3000), (8, 1, 3, 20000), (4, 4, 300, 60)])
+def test_decode_step_equals_cache_write_then_decode(cuda_device, hq, hkv, num_seqs, hi):
+    """aici_decode_step (cache write and decode overlapped in one call) against the two separate
+    calls on a copy of the same cache: caches bit-identical, outputs bit-identical; several times in
+    a row so that the overlap meets different timings.  The new token's slot is read by the decode."""
+    dev = cuda_device
+    w = workloads.make_decode("s", dev, num_seqs=num_seqs, num_heads=hq, num_kv_heads=hkv, ctx_kind="uniform",
+                              ctx_lo=1, ctx_hi=hi, pool_blocks=num_seqs * ((hi + 15) // 16) + 8, seed=400 + hq)
+    kc2, vc2 = w.key_cache.clone(), w.value_cache.clone()
+    ref = torch.empty_like(w.query)
+    tch_cuda.reshape_and_cache(w.new_key, w.new_value, kc2, vc2, w.slot_mapping)
+    tch_cuda.paged_attention_v1(ref, w.query, kc2, vc2, hkv, w.scale, w.block_tables, w.context_lens, 16,
+                                w.max_context_len, None)
+    for rep in range(4):
+        kc1, vc1 = w.key_cache.clone(), w.value_cache.clone()
+        got = torch.full_like(w.query, float("nan"))
+        tch_cuda.decode_step(got, w.new_key, w.new_value, w.slot_mapping, w.query, kc1, vc1, hkv, w.scale,
+                             w.block_tables, w.context_lens, 16, w.max_context_len)
+        torch.cuda.synchronize()
+        assert torch.equal(kc1.view(torch.int16), kc2.view(torch.int16)), rep
+        assert torch.equal(vc1.view(torch.int16), vc2.view(torch.int16)), rep
+        assert torch.equal(got.view(torch.int16), ref.view(torch.int16)), rep
+    want = O.paged_attention_v1(w.query.cpu(), kc2.cpu(), vc2.cpu(), hkv, w.scale, w.block_tables.cpu(),
+                                w.context_lens.cpu())
+    _check(got.cpu(), want)
+    assert _lib.last_status() == 0
+
+
+def test_decode_step_refuses_a_slot_that_is_not_the_last_position(cuda_device):
+    """The overlap is safe only because the write touches nothing but each sequence's last tile: a slot
+    anywhere else is recorded and not written."""
+    dev = cuda_device
+    w = workloads.make_decode("s", dev, num_seqs=5, num_heads=8, num_kv_heads=2, ctx_kind="uniform",
+                              ctx_lo=40, ctx_hi=400, pool_blocks=200, seed=411)
+    slots = w.slot_mapping.clone()
+    slots[2] = int(w.block_tables[2, 0]) * 16 + 3  # first block of the sequence instead of its last position
+    slots[4] = -1                                  # a skipped token stays allowed
+    kc, vc = w.key_cache.clone(), w.value_cache.clone()
+    out = torch.empty_like(w.query)
+    tch_cuda.decode_step(out, w.new_key, w.new_value, slots, w.query, kc, vc, 2, w.scale, w.block_tables,
+                         w.context_lens, 16, w.max_context_len)
+    torch.cuda.synchronize()
+    assert _lib.last_status() == 2  # AICI_STATUS_BAD_SLOT
+    kc_want, vc_want = w.key_cache.clone(), w.value_cache.clone()
+    keep = torch.tensor([0, 1, 3], device=dev)
+    tch_cuda.reshape_and_cache(w.new_key[keep].contiguous(), w.new_value[keep].contiguous(), kc_want, vc_want,
+                               w.slot_mapping[keep].contiguous())
+    assert torch.equal(kc.view(torch.int16), kc_want.view(torch.int16))
+    assert torch.equal(vc.view(torch.int16), vc_want.view(torch.int16))
