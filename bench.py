@@ -852,9 +852,10 @@ def run_ours(args):
                         "resident state" + ("; steps alternate between two peer-mapped output buffers, so a "
                                             "peer's next step never writes what this rank still reads"
                                             if fused else "")},
-        # this library's kernels inside the timed region, per step: reshape_and_cache, paged_decode,
-        # paged_merge (whose tail is the cross-GPU barrier when the fused gather is used)
-        "gpu_launches": 3 * args.steps,
+        # this library's kernels inside the timed region, per step: paged_decode (which also writes the
+        # step's new tokens to the cache) and paged_merge (whose tail is the cross-GPU barrier when the
+        # fused gather is used); with --separate-calls reshape_and_cache is a third launch
+        "gpu_launches": (3 if args.separate_calls else 2) * args.steps,
         "clocks": clocks,
         "parity": parity,
         "configs": configs,
