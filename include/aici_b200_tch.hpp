@@ -411,6 +411,42 @@ inline void paged_attention_v1(Tensor &out, const Tensor &query, const Tensor &k
                                     detail::dtype_of(fn, query), stream));
 }
 
+// One decode step of one layer: reshape_and_cache of the step's new tokens (token i = newest token
+// of sequence i, slot_mapping[i] = the cache slot of position context_lens[i] - 1) and
+// paged_attention_v1, the pair of crate calls rLLM makes per layer (llm/mod.rs:132-166, 280-316), as
+// one library call (aici_decode_step): the decode kernel writes the tokens to the cache itself.
+inline void decode_step(Tensor &out, const Tensor &new_key, const Tensor &new_value, const Tensor &slot_mapping,
+                        const Tensor &query, Tensor &key_cache, Tensor &value_cache, int num_kv_heads,
+                        float scale, const Tensor &block_tables, const Tensor &context_lens, int block_size,
+                        int max_context_len, cudaStream_t stream = cudaStreamPerThread) {
+  const char *fn = "decode_step";
+  const int dev = detail::require_cuda(fn, {&out, &new_key, &new_value, &slot_mapping, &query, &key_cache,
+                                            &value_cache, &block_tables, &context_lens});
+  const detail::DecodeDims d = detail::decode_dims(fn, out, query, key_cache, value_cache, num_kv_heads,
+                                                   block_tables, context_lens, block_size);
+  detail::require(fn, new_key.dim() == 3 && new_key.sizes == new_value.sizes && new_key.size(0) == d.num_seqs &&
+                          new_key.size(1) == num_kv_heads && new_key.size(2) == d.c.head_size,
+                  "new key/value must be [num_seqs, num_kv_heads, head_size]");
+  detail::require(fn, new_key.stride(2) == 1 && new_key.stride(1) == new_key.size(2) && new_value.stride(2) == 1 &&
+                          new_value.stride(1) == new_value.size(2),
+                  "heads of one token must be contiguous");
+  detail::require(fn, (slot_mapping.kind == Kind::Int || slot_mapping.kind == Kind::Int64) &&
+                          slot_mapping.is_contiguous() && slot_mapping.numel() == d.num_seqs,
+                  "slot_mapping must be contiguous int32 or int64 with one entry per sequence");
+  detail::DeviceGuard guard(dev);
+  const size_t need = aici_paged_attention_workspace_bytes(d.num_seqs, d.num_heads, num_kv_heads, max_context_len);
+  size_t have = 0;
+  void *ws = detail::decode_workspace(dev, stream, need, &have);
+  void *outs[1] = {out.data};
+  check(fn, aici_decode_step(outs, nullptr, 1, 0, d.num_heads, 0, new_key.data, new_value.data, slot_mapping.data,
+                             slot_mapping.kind == Kind::Int64 ? 1 : 0, new_key.stride(0), new_value.stride(0),
+                             query.data, key_cache.data, value_cache.data, num_kv_heads, scale,
+                             static_cast<const int32_t *>(block_tables.data),
+                             static_cast<const int32_t *>(context_lens.data), block_size, max_context_len,
+                             d.num_seqs, d.num_heads, d.c.head_size, d.max_blocks, d.c.num_blocks, query.stride(0),
+                             key_cache.stride(0), key_cache.stride(1), ws, have, detail::dtype_of(fn, query), stream));
+}
+
 // The extern's argument list (lib.rs:122-137): exp_sums / max_logits f32 [num_seqs, num_heads, P],
 // tmp_out [num_seqs, num_heads, P, head_size] in the query's dtype, P = ceil(max_context_len / 512).
 inline void paged_attention_v2(Tensor &out, Tensor &exp_sums, Tensor &max_logits, Tensor &tmp_out,

@@ -215,6 +215,34 @@ static void paged_attention_matches_oracle(bool v2) {
   EXPECT(t::last_status() == 0, "status word set");
 }
 
+// One call for the whole decode step against the two crate calls: same cache, same output, bit for bit.
+static void decode_step_equals_cache_write_then_decode() {
+  Rng r(27);
+  const int hq = 8, hkv = 2;
+  const std::vector<int> lens = {1, 16, 17, 300, 513, 1100, 47, 32};
+  Paged p(r, 160, hkv, lens);
+  const int S = (int)lens.size();
+  auto q = randn_bf16(r, (size_t)S * hq * 128);
+  auto nk = randn_bf16(r, (size_t)S * hkv * 128), nv = randn_bf16(r, (size_t)S * hkv * 128);
+  std::vector<int32_t> slots(S);
+  for (int s = 0; s < S; ++s) slots[s] = p.tables[(size_t)s * p.max_blocks + (lens[s] - 1) / 16] * 16 + (lens[s] - 1) % 16;
+  const float scale = 0.0884f;
+  Tensor dq = to_device(q, {S, hq, 128}, Kind::BFloat16);
+  Tensor dk = to_device(nk, {S, hkv, 128}, Kind::BFloat16), dv = to_device(nv, {S, hkv, 128}, Kind::BFloat16);
+  Tensor ds = to_device(slots, {S}, Kind::Int);
+  Tensor bt = to_device(p.tables, {S, p.max_blocks}, Kind::Int), cl = to_device(p.ctx, {S}, Kind::Int);
+  Tensor kc_a = p.key_cache(), vc_a = p.value_cache(), kc_b = p.key_cache(), vc_b = p.value_cache();
+  Tensor out_a = Tensor::empty({S, hq, 128}, Kind::BFloat16, 0), out_b = Tensor::empty({S, hq, 128}, Kind::BFloat16, 0);
+  t::reshape_and_cache(dk, dv, kc_a, vc_a, ds);
+  t::paged_attention_v1(out_a, dq, kc_a, vc_a, hkv, scale, bt, cl, 16, p.max_ctx);
+  t::decode_step(out_b, dk, dv, ds, dq, kc_b, vc_b, hkv, scale, bt, cl, 16, p.max_ctx);
+  EXPECT(to_host<uint16_t>(kc_a) == to_host<uint16_t>(kc_b), "key caches differ");
+  EXPECT(to_host<uint16_t>(vc_a) == to_host<uint16_t>(vc_b), "value caches differ");
+  EXPECT(to_host<uint16_t>(out_a) == to_host<uint16_t>(out_b), "outputs differ");
+  EXPECT(to_host<uint16_t>(kc_a) != p.kc, "the step wrote nothing");
+  EXPECT(t::last_status() == 0, "status word set");
+}
+
 static void copy_blocks_matches_oracle() {
   Rng r(31);
   const int layers = 3, nblk = 24, hkv = 2;
@@ -472,6 +500,7 @@ int main(int argc, char **argv) {
       {"reshape_and_cache_then_gather_round_trip", reshape_and_cache_then_gather_round_trip},
       {"paged_attention_v1_matches_oracle", [] { paged_attention_matches_oracle(false); }},
       {"paged_attention_v2_matches_oracle", [] { paged_attention_matches_oracle(true); }},
+      {"decode_step_equals_cache_write_then_decode", decode_step_equals_cache_write_then_decode},
       {"copy_blocks_matches_oracle", copy_blocks_matches_oracle},
       {"swap_blocks_out_and_in", swap_blocks_out_and_in},
       {"flash_attn_varlen_causal_ragged_gqa", [] { flash_attn_varlen_case({64, 130, 1, 257}, {64, 130, 1, 257}, 8, 2, true, false); }},
