@@ -17,6 +17,9 @@
 //     fp32 partial (max, sum, normalised output) that a merge kernel combines.
 // So K/V are read from HBM exactly once per (sequence, kv head) regardless of the group
 // size and every byte moves as a 4 KB contiguous burst.
+// Two things a decode step needs besides attention can ride on these kernels: the cache write of the
+// step's new tokens (aici_decode_step: the warp that reaches a row's last tile writes the token) and,
+// with kv heads sharded over GPUs, the ranks' barrier (run by the last CTA of the merge kernel).
 // Two ways of cutting the batch into pieces exist.  "Spans" (the default of the v1 entry): the
 // tiles of the whole batch are laid end to end and every warp of the grid takes one run of the
 // same length, so the load is even whatever the context lengths are (next_piece).  "Chunks": every

@@ -7,7 +7,10 @@
 // head / (num_heads / num_heads_k), causal mask aligned to the bottom-right corner
 // (softmax.h:159-168), rows that see no column give 0 (flash_fwd_kernel.h:1056).
 //
-// One CTA per SM owns TWO 128-row query tiles that share their key/value tiles: two query heads
+// The kernel comes in three shapes (PrefillCfg below): one query tile per CTA with two CTAs per SM
+// for short sequences, two query tiles per CTA for long ones, and the two-tile shape on pairs of
+// CTAs whose MMAs span two SMs.  The roles, in the two-tile shape:
+// one CTA per SM owns TWO 128-row query tiles that share their key/value tiles: two query heads
 // of one kv-head group when the group size is even (same rows, same causal extent), else two
 // consecutive row tiles of one head.  Each key/value tile of 128 tokens is loaded once for both.
 //   warp 8    : TMA producer (Q0, Q1 once; then K_0, V_0, K_1, V_1, ... through a 4-stage ring of
@@ -22,6 +25,8 @@
 //               row sum, and a tile whose scores jump too far is redone exactly), bf16 P written
 //               back with tcgen05.st; at the end O / sum -> bf16 -> staging in the tile's Q buffer
 //               (same swizzled layout) -> TMA stores, or row-by-row stores for a ragged tile.
+// (One-tile shape: warps 0-3 softmax, warp 4 producer, warp 5 issuer.)  The grid is ordered
+// (head, sequence, row tile), row tile slowest and longest first.
 // Every barrier wait is bounded; a timeout sets AICI_STATUS_WAIT_TIMEOUT and unwinds.
 #include "tcgen05.cuh"
 

@@ -194,10 +194,16 @@ class PeerMemory:
         """Unmaps the peers' blocks, meets the other ranks, frees the own block (in that order: a
         block must not be freed while a peer still has it mapped)."""
         lib = self._lib.lib()
+
+        def quietly(name, res):  # tear-down goes on past an error, but the message must not leak
+            try:
+                self._lib.check(name, res)
+            except self._lib.AiciError:
+                pass
         with torch.cuda.device(self.device):
             torch.cuda.synchronize(self.device)
             for p in self._opened:
-                lib.aici_peer_close(ctypes.c_void_p(p))
+                quietly("aici_peer_close", lib.aici_peer_close(ctypes.c_void_p(p)))
             self._opened = []
             if meet and dist.is_initialized():
                 try:
@@ -205,7 +211,7 @@ class PeerMemory:
                 except Exception:  # noqa: BLE001 - a dead peer must not keep this rank from freeing
                     pass
             if self._own.value:
-                lib.aici_peer_free(self._own)
+                quietly("aici_peer_free", lib.aici_peer_free(self._own))
                 self._own = ctypes.c_void_p(0)
         self.ptrs = []
 
