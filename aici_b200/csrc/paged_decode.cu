@@ -547,34 +547,60 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const Dec
   const bool work = active && n > 1;  // n == 1: the decode kernel wrote the row itself
   float wsum = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
   if (work) {
+    const PartT *po = static_cast<const PartT *>(p.part_out) + base * kD + 4 * lane;
+    auto load_row = [&](int64_t j) {  // lane's four values of partial j of this row
+      if (sizeof(PartT) == 4) return *reinterpret_cast<const float4 *>(po + j * pstride * kD);
+      const uint2 raw = *reinterpret_cast<const uint2 *>(po + j * pstride * kD);
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x);
+      const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
+      return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+    };
+    // Everything the first batch needs is asked for at once -- the maxima of all partials, the
+    // maximum and sum of the partials this lane weighs, and the first rows themselves -- so that a
+    // row with a handful of partials costs one trip to memory, not one per step of the formula.
+    constexpr int kAhead = kTeam == 1 ? 8 : 2;
+    const int cnt0 = tw < n ? min(32, (n - tw + kTeam - 1) / kTeam) : 0;
     float m = -INFINITY;
     for (int j = lane; j < n; j += 32) m = fmaxf(m, p.part_max[base + (int64_t)j * pstride]);
+    float pm = 0.f, ps = 0.f;
+    if (lane < cnt0) {
+      const int64_t j = base + (int64_t)(tw + kTeam * lane) * pstride;
+      pm = p.part_max[j];
+      ps = p.part_sum[j];
+    }
+    float4 ahead[kAhead];
+#pragma unroll
+    for (int l = 0; l < kAhead; ++l)
+      ahead[l] = l < cnt0 ? load_row(tw + kTeam * l) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const PartT *po = static_cast<const PartT *>(p.part_out) + base * kD + 4 * lane;
     // this warp's partials: tw, tw + kTeam, ...; lane l prepares the weight of partial tw + kTeam l
     for (int j0 = tw; j0 < n; j0 += kTeam * 32) {
       const int cnt = min(32, (n - j0 + kTeam - 1) / kTeam);
       float w_lane = 0.f;
-      if (lane < cnt) {
+      if (j0 == tw) {
+        if (lane < cnt) w_lane = ps * __expf(pm - m);
+      } else if (lane < cnt) {
         const int64_t j = base + (int64_t)(j0 + kTeam * lane) * pstride;
         w_lane = p.part_sum[j] * __expf(p.part_max[j] - m);
       }
-#pragma unroll 4
-      for (int l = 0; l < cnt; ++l) {
-        const float w = __shfl_sync(0xffffffffu, w_lane, l);
-        const int64_t j = (int64_t)(j0 + kTeam * l) * pstride;
-        wsum += w;
-        if (sizeof(PartT) == 4) {
-          const float4 v = *reinterpret_cast<const float4 *>(po + j * kD);
-          a0 += w * v.x; a1 += w * v.y; a2 += w * v.z; a3 += w * v.w;
-        } else {
-          const uint2 raw = *reinterpret_cast<const uint2 *>(po + j * kD);
-          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x);
-          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
-          a0 += w * __low2float(lo); a1 += w * __high2float(lo);
-          a2 += w * __low2float(hi); a3 += w * __high2float(hi);
+      int l = 0;
+      if (j0 == tw) {
+#pragma unroll
+        for (; l < kAhead; ++l) {
+          if (l < cnt) {
+            const float w = __shfl_sync(0xffffffffu, w_lane, l);
+            wsum += w;
+            a0 += w * ahead[l].x; a1 += w * ahead[l].y; a2 += w * ahead[l].z; a3 += w * ahead[l].w;
+          }
         }
+      }
+#pragma unroll 4
+      for (; l < cnt; ++l) {
+        const float w = __shfl_sync(0xffffffffu, w_lane, l);
+        const float4 v = load_row(j0 + kTeam * l);
+        wsum += w;
+        a0 += w * v.x; a1 += w * v.y; a2 += w * v.z; a3 += w * v.w;
       }
     }
   }

@@ -473,20 +473,28 @@ def run_ours(args):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     prof = torch.cuda.cudart() if args.profile_step is not None else None
 
-    def timed_steps(runs, steps, profile=False):
+    def timed_steps(runs, steps, profile=False, group=None):
         """`steps` back-to-back steps between two events -> (device ms, host wall ms).  With
         `profile`, one step is bracketed by the profiler API (cudaProfilerStart/Stop, as rLLM's
-        --profile-step does around one forward pass, so that a capture can be limited to it)."""
+        --profile-step does around one forward pass, so that a capture can be limited to it).
+        `group` = (replay, n): one graph that holds n consecutive steps, used for as many whole
+        groups as fit; the remaining steps go one by one."""
         R.barrier()
         t0 = time.perf_counter()
         ev0.record()
-        for i in range(steps):
+        i = 0
+        while i < steps:
+            if group is not None and i + group[1] <= steps:
+                group[0]()
+                i += group[1]
+                continue
             mark = profile and prof is not None and i == args.profile_step
             if mark:
                 prof.cudaProfilerStart()
             runs[i % len(runs)]()
             if mark:
                 prof.cudaProfilerStop()
+            i += 1
         ev1.record()
         ev1.synchronize()
         wall = (time.perf_counter() - t0) * 1e3
@@ -498,10 +506,24 @@ def run_ours(args):
         runs = [g.replay for g in graphs]
     else:
         runs = [(lambda i=i: step(i)) for i in range(n_graphs)]
+    # The forward pass of a model issues one such step per layer inside one graph; the timed steps
+    # are submitted the same way, several to a graph (a whole number of turns through the pools and
+    # output buffers), unless one step is to be bracketed for a profiler.
+    spg = args.steps_per_graph if args.steps_per_graph > 0 else max(n_graphs, 4)
+    if spg > 1:
+        spg = (spg + n_graphs - 1) // n_graphs * n_graphs
+    group = None
+    if use_graph and spg > 1 and args.profile_step is None:
+        group = (R.capture(lambda: [step(i) for i in range(spg)]).replay, spg)
+    else:
+        spg = 1
     for i in range(3 * n_graphs):
         runs[i % n_graphs]()
+    if group is not None:
+        for _ in range(2):
+            group[0]()
     sampler.region("decode")
-    ms_total = R.max_over_ranks(timed_steps(runs, args.steps, profile=True)[0])
+    ms_total = R.max_over_ranks(timed_steps(runs, args.steps, profile=True, group=group)[0])
     ms_step = ms_total / args.steps
 
     # The decode call alone (decode + merge launches; with the fused gather their stores to the
@@ -850,7 +872,7 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": config,
         "run": {
-            "launch": "one CUDA-graph replay per step" if use_graph else "eager launches",
+            "launch": ("CUDA-graph replays, %d steps per graph" % spg) if use_graph else "eager launches",
             "step_call": ("reshape_and_cache, then paged_attention_v1" if args.separate_calls else
                           "aici_decode_step (cache write and decode attention in one call, overlapped)"),
             "pool_copies": n_pools,
@@ -1208,6 +1230,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch the decode step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--steps-per-graph", type=int, default=0,
+                    help="timed decode steps held by one CUDA graph (0: one turn through the pool copies and "
+                         "output buffers, at least 4; 1: one graph replay per step)")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="multi-GPU head-output gather: fused into the attention epilogue (default) or NCCL")
     ap.add_argument("--separate-calls", action="store_true",
