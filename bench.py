@@ -53,6 +53,11 @@ MIN_STREAM_BYTES = 1 << 30
 # the 16-sequence case of `--profile decode`; traffic grows in proportion to the tokens read).  The
 # summaries are under profiles/.  A world size without a capture reports no traffic figure.
 DECODE_TRAFFIC_RATIO = {1: 1.011, 2: 1.007, 4: 1.010, 8: 1.015}
+# DRAM bytes (read + write) of one full-size varlen_prefill_kernel launch (2 x 32768, 64/8 heads) on
+# one GPU: a one-pass ncu capture of `--profile prefill_full` (15.93 GB read, 1.18 GB written, for
+# 2.42 GB of q, k, v and output: the two sequences' K/V, 268 MB, do not fit the L2 and are fetched
+# again by later row tiles; 0.58 TB/s, 9 % of the HBM rate).  Shards of 2, 4, 8 GPUs were not captured.
+PREFILL_TRAFFIC_BYTES = {1: 17.11e9}
 
 
 def load_peaks():
@@ -918,9 +923,12 @@ def run_ours(args):
                          "frac": p_kernel_tflops / peaks["bf16_tflops_sustained"],
                          "frac_of_burst_peak": p_kernel_tflops / peaks["bf16_tflops"],
                          "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "launch_ms": p_kernel_ms,
-                         "traffic": None,
-                         "traffic_note": "not captured: the 2 x 4096 capture (5.6 % DRAM utilisation, K/V served "
-                                         "from L2) does not scale to 268 MB of K/V against a 126 MB L2"},
+                         "traffic": PREFILL_TRAFFIC_BYTES.get(world),
+                         "traffic_note": ("ncu dram read+write of this launch (one-pass capture of `--profile "
+                                          "prefill_full`); q, k, v and output are 2.42 GB, the rest is K/V "
+                                          "fetched again by later row tiles (268 MB of K/V against a 126 MB L2), "
+                                          "9 % of the HBM rate" if world in PREFILL_TRAFFIC_BYTES else
+                                          "not captured at this world size")},
             "clocks": sampler.summary("prefill"),
         },
     }
@@ -1214,12 +1222,17 @@ def run_profile_case(args):
         torch.cuda.synchronize()
         print(json.dumps({"profile_case": "prefill_chunks", "flops": pw.flops()}))
     else:
-        pw = workloads.prefill_long(dev, seqlen=4096)
-        for _ in range(3):
+        # prefill_full: the benchmark's own 2 x 32768 launch (2.4 GB on the device, 33 ms), twice; only
+        # for captures that take one pass (DRAM byte counters), so that nothing is saved or restored
+        seqlen, reps = (32768, 2) if args.profile == "prefill_full" else (4096, 3)
+        pw = workloads.prefill_long(dev, seqlen=seqlen)
+        for _ in range(reps):
             tch_cuda.flash_attn_varlen(pw.q, pw.k, pw.v, pw.cu_seqlens_q, pw.cu_seqlens_k, pw.max_seqlen_q,
                                        pw.max_seqlen_k, pw.scale, True)
         torch.cuda.synchronize()
-        print(json.dumps({"profile_case": "prefill", "seqlen": 4096, "flops": pw.flops()}))
+        io = sum(t.numel() * t.element_size() for t in (pw.q, pw.k, pw.v)) + pw.q.numel() * pw.q.element_size()
+        print(json.dumps({"profile_case": args.profile, "seqlen": seqlen, "flops": pw.flops(),
+                          "q_k_v_out_bytes": io}))
 
 
 def main():
@@ -1245,7 +1258,7 @@ def main():
                          "(what rLLM's --profile-step does), for captures limited to the profiler API range")
     ap.add_argument("--suite", action="store_true",
                     help="time all five configurations at the current world size and print one JSON object")
-    ap.add_argument("--profile", default=None, choices=["decode", "prefill", "prefill_chunks", "small_ops"],
+    ap.add_argument("--profile", default=None, choices=["decode", "prefill", "prefill_full", "prefill_chunks", "small_ops"],
                     help="run a small case three times for a profiler capture and exit")
     ap.add_argument("--profile-world", type=int, default=1,
                     help="with --profile decode: run rank 0's shard of a run on this many GPUs")
