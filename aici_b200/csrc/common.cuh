@@ -156,6 +156,23 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t *bar, uint32_t pari
   return true;
 }
 
+// Waits, bounded to about a second, until the counter at `slot` (added to by a peer at system
+// scope; it wraps, so the difference is what is compared) has reached `target`.  A peer that never
+// gets there is recorded as AICI_STATUS_PEER_TIMEOUT and the thread returns.
+__device__ __forceinline__ void peer_wait_count(const unsigned int *slot, unsigned int target,
+                                                unsigned int *status) {
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(slot) : "memory");
+    if ((int)(v - target) >= 0) return;
+    if (clock64() - t0 > (1ll << 31)) {
+      set_status(status, AICI_STATUS_PEER_TIMEOUT);
+      return;
+    }
+  }
+}
+
 // Barrier between the GPUs that share peer-mapped flag arrays, executed by the first `world` threads
 // of one warp: thread p publishes `epoch` into slot `rank` of rank p's array (release store at
 // system scope; the caller has fenced its own earlier stores) and waits, bounded to about a second,

@@ -19,7 +19,8 @@
 // size and every byte moves as a 4 KB contiguous burst.
 // Two things a decode step needs besides attention can ride on these kernels: the cache write of the
 // step's new tokens (aici_decode_step: the warp that reaches a row's last tile writes the token) and,
-// with kv heads sharded over GPUs, the ranks' barrier (run by the last CTA of the merge kernel).
+// with kv heads sharded over GPUs, the ranks' barrier (every CTA of the merge kernel reports to all
+// ranks when its rows are stored, one CTA waits for all reports).
 // Two ways of cutting the batch into pieces exist.  "Spans" (the default of the v1 entry): the
 // tiles of the whole batch are laid end to end and every warp of the grid takes one run of the
 // same length, so the load is even whatever the context lengths are (next_piece).  "Chunks": every
@@ -64,7 +65,9 @@ struct DecodeParams {
   int max_parts;
   int always_write_partials;  // v2 calling convention: partials are an output too
   int inline_plan;            // 1: every CTA builds the chunk prefix sums itself (no plan kernel)
-  int *span_cum;              // spans mode: [num_seqs + 2] tile prefix sums, then the span length
+  int decode_warps;           // spans mode: warps of the decode grid (the merge kernel derives the span length from it)
+  int *span_cum;              // spans mode, large merge grids: [num_seqs + 2] tile prefix sums, then the span length
+  int early_sums;             // spans mode: 1 = the merge CTAs add the context lengths up themselves
   int min_span;               // spans mode: fewest tiles a warp takes
   int64_t q_stride, kv_block_stride, kv_head_stride;
   float scale_log2e;
@@ -201,10 +204,12 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
   }
   __syncwarp();
 
-  // Programmatic dependent launch: let the merge grid get resident early, and (when this grid was
-  // itself launched as a dependent of the plan kernel) wait for the chunk list before reading it.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Programmatic dependent launch: wait for the grid before this one (its writes -- context
+  // lengths, the chunk list of the plan kernel, anything else -- are visible from here on), then let
+  // the merge grid get resident.  In this order the merge grid, which reads the context lengths
+  // before its own wait, cannot start while a producer of those lengths is still running.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   int *s_cum = reinterpret_cast<int *>(smem + kWarps * kStages * kStageBytes + kWarps * kStages * sizeof(uint64_t));
   if (p.inline_plan) {
     // chunk-count prefix sums over the batch, built by every CTA for itself: all threads fetch
@@ -246,7 +251,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
     const int64_t x0 = (int64_t)gw * span;
     p_cur.x = c_cur.x = x0 < n_items ? (int)x0 : n_items;
     p_cur.end = c_cur.end = x0 + span < n_items ? (int)(x0 + span) : n_items;
-    if (blockIdx.x == 0 && warp == 0) {  // what the merge kernel needs to find the pieces of a row
+    if (!p.early_sums && blockIdx.x == 0 && warp == 0) {  // what a large merge grid needs to find the pieces of a row
       for (int i = lane; i <= p.num_seqs; i += 32) p.span_cum[i] = s_cum[i];
       if (lane == 0) p.span_cum[p.num_seqs + 1] = span;
     }
@@ -505,14 +510,14 @@ __global__ void __launch_bounds__(kWarps * 32, 2) paged_decode_kernel(const Deco
 // shuffle, so the 512-byte row loads of a warp are independent -- and the team's sums meet in
 // shared memory.  Lane l owns d = 4l .. 4l+3.  kTeam = 8 (one row per CTA) suits rows with many
 // partials; kTeam = 1 (eight rows per CTA) suits the spans mode with large batches, where a row
-// has two or three.  In spans mode the partials of a row are consecutive pieces (see next_piece).
+// has two or three; 2 and 4 lie between (launch_decode picks).  In spans mode the partials of a row
+// are consecutive pieces (see next_piece).
 constexpr int kMergeWarps = 8;
 template <typename PartT, bool kSpans, int kTeam>
 __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const DecodeParams p) {
   // a grid launched as a programmatic dependent of this one (the next step's cache write, the next
   // decode call) may become resident now; it waits for this grid before it touches anything
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");  // no-op unless launched as a dependent grid
   constexpr int kRows = kMergeWarps / kTeam;
   __shared__ float s_acc[kMergeWarps][kD];
   __shared__ float s_w[kMergeWarps];
@@ -521,12 +526,56 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const Dec
   const int row = blockIdx.x * kRows + team;
   const bool active = row < p.num_seqs * p.num_heads;
   const int seq = active ? row / p.num_heads : 0, head = active ? row - seq * p.num_heads : 0;
+  // Spans mode: where the pieces of a row lie follows from the context lengths alone (tiles before
+  // its sequence, tiles of its sequence, tiles of the batch).  The lengths are an input of the call,
+  // complete before the decode grid let this grid in, so a CTA that is resident beside the decode
+  // grid adds them up while that grid still runs (one warp, once per length).  The host asks for
+  // this only when the whole merge grid fits beside the decode grid; the CTAs of a larger grid
+  // start after it and are better served by three loads of what decode CTA 0 left in the workspace.
+  int c0 = 0, tiles = 0, total = 0;
+  if (kSpans && p.early_sums) {
+    __shared__ int s_pre[2 + kRows];  // tiles of the batch, tiles before the CTA's first sequence, tiles of its sequences
+    const int row_first = blockIdx.x * kRows;
+    const int seq_first = min(row_first / p.num_heads, p.num_seqs - 1);
+    if (warp == 0) {
+      int before = 0, all = 0;
+      for (int s0 = lane; s0 < p.num_seqs; s0 += 32) {
+        const int t = (clamp_ctx(p, p.context_lens[s0]) + kB - 1) / kB;
+        all += t;
+        if (s0 < seq_first) before += t;
+        if (s0 >= seq_first && s0 < seq_first + kRows) s_pre[2 + s0 - seq_first] = t;
+      }
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) {
+        all += __shfl_xor_sync(0xffffffffu, all, o);
+        before += __shfl_xor_sync(0xffffffffu, before, o);
+      }
+      if (lane == 0) {
+        s_pre[0] = all;
+        s_pre[1] = before;
+      }
+    }
+    __syncthreads();
+    total = s_pre[0];
+    c0 = s_pre[1];
+    for (int s0 = seq_first; s0 < seq; ++s0) c0 += s_pre[2 + s0 - seq_first];  // at most kRows - 1 terms
+    tiles = active ? s_pre[2 + seq - seq_first] : 0;
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // no-op unless launched as a dependent grid
   int n = 0, pstride = 1;
   int64_t base = 0;
   if (active) {
     if (kSpans) {
-      const int c0 = p.span_cum[seq], tiles = p.span_cum[seq + 1] - c0;
-      const int span = p.span_cum[p.num_seqs + 1];
+      int span;
+      if (p.early_sums) {
+        const int64_t n_items = (int64_t)total * p.num_kv_heads;
+        span = (int)((n_items + p.decode_warps - 1) / p.decode_warps);
+        if (span < p.min_span) span = p.min_span;
+      } else {
+        c0 = p.span_cum[seq];
+        tiles = p.span_cum[seq + 1] - c0;
+        span = p.span_cum[p.num_seqs + 1];
+      }
       if (tiles > 0) {
         const int kvh = head / p.group;
         const int g0 = p.num_kv_heads * c0 + kvh * tiles;
@@ -558,7 +607,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const Dec
     // Everything the first batch needs is asked for at once -- the maxima of all partials, the
     // maximum and sum of the partials this lane weighs, and the first rows themselves -- so that a
     // row with a handful of partials costs one trip to memory, not one per step of the formula.
-    constexpr int kAhead = kTeam == 1 ? 8 : 2;
+    constexpr int kAhead = kTeam == 1 ? 4 : 2;  // more would cost registers, and with them resident CTAs
     const int cnt0 = tw < n ? min(32, (n - tw + kTeam - 1) / kTeam) : 0;
     float m = -INFINITY;
     for (int j = lane; j < n; j += 32) m = fmaxf(m, p.part_max[base + (int64_t)j * pstride]);
@@ -624,31 +673,31 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const Dec
     for (int w = 0; w < p.world; ++w) *reinterpret_cast<uint2 *>(p.out[w] + out_off) = packed;
   }
   if (p.sync) {
-    // Fused head-gather barrier: the rows of this call are in every rank's buffer once all CTAs of
-    // this grid are through (the decode grid before it has completed: griddepcontrol.wait above).
-    // CTAs count themselves off in slot 9 of this rank's flag array; the last one resets the count
-    // (so that the launch can be replayed), takes the next epoch from slot 8 and runs the barrier
-    // of aici_peer_barrier on the lanes of its first warp.  The grid ends when every peer has
-    // signalled (or after the bounded wait), so work queued behind it may read all heads.
-    __shared__ unsigned int s_epoch, s_last;
+    // Fused head-gather barrier.  Every CTA, once its rows are stored, tells every rank so itself:
+    // a system-scope fence (the rows are in the peers' memory) and one relaxed add per rank into
+    // slot 16 + rank of that rank's flag array.  The CTAs of a grid add up to exactly 2^20 per call
+    // whatever the grid size, so after k such calls a rank has 2^20 k from every peer that has
+    // finished (counters wrap; differences are compared).  CTA 0 is the one that waits: lane p of
+    // its first warp until slot 16 + p of this rank's own array has reached this call's target,
+    // bounded to about a second.  The count of calls lives in slot 10 of the rank's own array, so a
+    // launch can be replayed.  No CTA waits for another CTA of its own grid through memory of this
+    // GPU first, which is what made the former count-then-signal version a round trip longer.
     __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned int *mine = p.peer_flags[p.rank];
-      unsigned int last = 0, epoch = 0;
+    if (threadIdx.x < p.world) {
+      const unsigned int lo = (unsigned int)(((uint64_t)blockIdx.x << 20) / gridDim.x);
+      const unsigned int hi = (unsigned int)(((uint64_t)(blockIdx.x + 1) << 20) / gridDim.x);
       __threadfence_system();  // cumulative: covers the stores of the whole CTA (ordered by the barrier above)
-      if (atomicAdd(mine + 9, 1u) == gridDim.x - 1) {
-        atomicExch(mine + 9, 0u);
-        epoch = mine[8] + 1;
-        mine[8] = epoch;
-        __threadfence_system();
-        last = 1;
-      }
-      s_epoch = epoch;
-      s_last = last;
+      asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.peer_flags[threadIdx.x] + 16 + p.rank),
+                   "r"(hi - lo)
+                   : "memory");
     }
-    __syncthreads();
-    if (s_last && threadIdx.x < p.world)
-      peer_signal_and_wait(p.peer_flags, p.rank, threadIdx.x, s_epoch, p.status);
+    if (blockIdx.x == 0 && threadIdx.x < 32) {
+      unsigned int *mine = p.peer_flags[p.rank];
+      const unsigned int calls = mine[10] + 1;
+      if (lane < p.world) peer_wait_count(mine + 16 + lane, calls << 20, p.status);
+      __syncwarp();
+      if (lane == 0) mine[10] = calls;
+    }
   }
 }
 
@@ -743,8 +792,8 @@ static WorkspaceLayout workspace_layout(int num_seqs, int num_heads, int max_con
   return w;
 }
 
-// Spans mode: tile prefix sums for the merge kernel, then one partial per piece and group head;
-// pieces are fewer than warps + rows whatever the context lengths are.
+// Spans mode: tile prefix sums for the merge kernel (used by large merge grids), then one partial
+// per piece and group head; pieces are fewer than warps + rows whatever the context lengths are.
 static WorkspaceLayout spans_layout(int num_seqs, int num_heads, int num_kv_heads) {
   WorkspaceLayout w;
   const size_t pieces = (size_t)2 * sm_count() * kWarps + (size_t)num_seqs * num_kv_heads;
@@ -809,6 +858,10 @@ static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaS
         // kernel of a decode step on one SM configuration.
         AICI_CUDA(cudaFuncSetAttribute(paged_merge_kernel<PartT, kSpans, 1>,
                                        cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        AICI_CUDA(cudaFuncSetAttribute(paged_merge_kernel<PartT, kSpans, 2>,
+                                       cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        AICI_CUDA(cudaFuncSetAttribute(paged_merge_kernel<PartT, kSpans, 4>,
+                                       cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         AICI_CUDA(cudaFuncSetAttribute(paged_merge_kernel<PartT, kSpans, kMergeWarps>,
                                        cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         return nullptr;
@@ -849,17 +902,30 @@ static char *launch_decode(DecodeParams &p, int2 *entries, int *n_entries, cudaS
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kWarps * 32);
   cfg.dynamicSmemBytes = smem;
+  const int rows = p.num_seqs * p.num_heads;
+  // How many warps share a row.  Many (sequence, kv head) rows per warp of the decode grid: a row
+  // has few partials and one warp merges it.  Fewer rows have more partials each and 2, 4 or 8 warps
+  // share a row -- as many as keep the grid within one CTA per SM where that is possible: one
+  // merge CTA fits an SM beside the decode grid's two (registers), and a CTA that is resident while
+  // the decode grid runs has everything but the partials ready when that grid ends.
+  int team = kMergeWarps;
+  if (kSpans && (int64_t)p.num_seqs * p.num_kv_heads * 4 >= (int64_t)grid * kWarps) team = 1;
+  else if (kSpans && rows > 2 * sm_count()) team = 2;
+  else if (kSpans && rows > sm_count()) team = 4;
+  const int merge_grid = (rows * team + kMergeWarps - 1) / kMergeWarps;
+  p.decode_warps = grid * kWarps;
+  p.early_sums = kSpans && merge_grid <= sm_count() ? 1 : 0;
   AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_decode_kernel<PartT, kSpans>, p));
   cfg.blockDim = dim3(kMergeWarps * 32);
   cfg.dynamicSmemBytes = 0;
-  const int rows = p.num_seqs * p.num_heads;
-  // many (sequence, kv head) rows per warp of the decode grid: a row has few partials, one warp
-  // merges it; few rows: a row has many partials, eight warps share it
-  if (kSpans && (int64_t)p.num_seqs * p.num_kv_heads * 4 >= (int64_t)grid * kWarps) {
-    cfg.gridDim = dim3((rows + kMergeWarps - 1) / kMergeWarps);
+  cfg.gridDim = dim3(merge_grid);
+  if (team == 1) {
     AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_merge_kernel<PartT, kSpans, 1>, p));
+  } else if (team == 2) {
+    AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_merge_kernel<PartT, kSpans, 2>, p));
+  } else if (team == 4) {
+    AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_merge_kernel<PartT, kSpans, 4>, p));
   } else {
-    cfg.gridDim = dim3(rows);
     AICI_CUDA(cudaLaunchKernelEx(&cfg, paged_merge_kernel<PartT, kSpans, kMergeWarps>, p));
   }
   return nullptr;
@@ -957,7 +1023,9 @@ static char *paged_attention_v1_impl(const char *fn, void *const *outs, int worl
   p.chunk_tokens = chunk;
   p.max_parts = w.max_parts;
   p.always_write_partials = 0;
+  p.decode_warps = 0;  // set by launch_decode, like early_sums
   p.span_cum = reinterpret_cast<int *>(ws + w.entries_off);
+  p.early_sums = 0;
   p.min_span = kMinSpanTiles;
   p.q_stride = q_stride;
   p.kv_block_stride = kv_block_stride;
@@ -1166,7 +1234,9 @@ extern "C" char *aici_paged_attention_v2(void *out, float *exp_sums, float *max_
   p.chunk_tokens = 512;  // PARTITION_SIZE of the reference
   p.max_parts = max_context_len > 0 ? (max_context_len + 511) / 512 : 1;
   p.always_write_partials = 1;
+  p.decode_warps = 0;
   p.span_cum = nullptr;
+  p.early_sums = 0;
   p.min_span = 1;
   p.q_stride = q_stride;
   p.kv_block_stride = kv_block_stride;

@@ -10,7 +10,7 @@
 namespace aici {
 
 struct PeerFlags {
-  unsigned int *flags[8];  // flags[p] = rank p's array of 16 slots (slot r is written by rank r)
+  unsigned int *flags[8];  // flags[p] = rank p's array of 32 slots (slot r < 8 is written by rank r)
 };
 
 // Slot 8 of a rank's own array is its private barrier counter: every barrier increments it and

@@ -10,8 +10,9 @@ and cu_seqlens are the same on every rank); afterwards every rank needs all head
 attention output, which is one all-gather.
 
 torch.distributed is the plumbing (backend "nccl" on GPUs; "gloo" in the CPU tests).  The
-peer-mapped buffers of the fused gather come from the library's own C ABI (CUDA IPC), not from
-torch: a host without libtorch maps them with the same four calls.
+peer-mapped buffers of the fused gather come from the library's own C ABI (CUDA virtual-memory
+allocations shared by file descriptor, CUDA IPC where that is unavailable), not from torch: a host
+without libtorch maps them with the same four calls.
 """
 import ctypes
 from typing import List, Optional
@@ -251,7 +252,7 @@ class PeerGather:
         self.tensors = [self.mem.view(self.FLAG_BYTES + i * self._buf_bytes, self.shape, dtype)
                         for i in range(buffers)]
         self._ptrs = [[p + self.FLAG_BYTES + i * self._buf_bytes for p in self.mem.ptrs] for i in range(buffers)]
-        self.flag_ptrs = list(self.mem.ptrs)  # the first 16 words of each block, zero after allocation
+        self.flag_ptrs = list(self.mem.ptrs)  # the first 32 words of each block, zero after allocation
         self.cur = 0
 
     @property

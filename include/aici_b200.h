@@ -252,9 +252,9 @@ char *aici_mha_varlen_fwd_peers(void *const *outs, int world, int head0, const v
                                 float softmax_scale, int is_causal, int dtype, aici_stream_t stream);
 
 /* Barrier between the ranks that share peer-mapped buffers (no counterpart in the reference).
- * flag_ptrs[p] = rank p's array of 16 uint32 slots in peer-mapped memory, all zero before the
- * first call; every rank must call it the same number of times (the epoch is a counter kept in the
- * array, so a captured launch can be replayed).  Enqueued on `stream`: work queued after it starts
+ * flag_ptrs[p] = rank p's array of 32 uint32 slots (128 bytes) in peer-mapped memory, all zero
+ * before the first call; every rank must call it the same number of times (the epoch is a counter
+ * kept in the array, so a captured launch can be replayed).  Enqueued on `stream`: work queued after it starts
  * once every rank's earlier work on its own stream has finished.  The wait is bounded (about a
  * second), then AICI_STATUS_PEER_TIMEOUT is recorded and the kernel returns. */
 char *aici_peer_barrier(void *const *flag_ptrs, int world, int rank, aici_stream_t stream);
@@ -262,7 +262,10 @@ char *aici_peer_barrier(void *const *flag_ptrs, int world, int rank, aici_stream
 /* aici_paged_attention_v1_peers with that barrier folded into its last kernel: when the call's
  * kernels have finished, every rank's buffer holds all heads, and no barrier launch follows (one
  * launch less per decode step).  flag_ptrs as for aici_peer_barrier; the two may be mixed on the
- * same arrays as long as all ranks make the same sequence of calls. */
+ * same arrays as long as all ranks make the same sequence of calls (this one counts arrivals in
+ * slots 16-23 and its calls in slot 10; the barrier kernel uses slots 0-8).  Every CTA of the last
+ * kernel reports to every rank once its rows are stored there, and one CTA waits until every rank
+ * has reported in full: bounded, AICI_STATUS_PEER_TIMEOUT as above. */
 char *aici_paged_attention_v1_peers_barrier(void *const *outs, void *const *flag_ptrs, int world,
                                             int rank, int total_heads, int head0, const void *query,
                                             const void *key_cache, const void *value_cache,

@@ -25,8 +25,8 @@ def _barrier(flags, rank):
 
 
 def test_barrier_passes_when_the_peer_has_arrived(cuda_device):
-    mine = torch.zeros(16, dtype=torch.int32, device=cuda_device)
-    peer = torch.zeros(16, dtype=torch.int32, device=cuda_device)
+    mine = torch.zeros(32, dtype=torch.int32, device=cuda_device)
+    peer = torch.zeros(32, dtype=torch.int32, device=cuda_device)
     mine[1] = 3  # "rank 1" already published epochs 1..3 into rank 0's array
     for epoch in (1, 2, 3):
         t0 = time.perf_counter()
@@ -38,8 +38,8 @@ def test_barrier_passes_when_the_peer_has_arrived(cuda_device):
 
 
 def test_barrier_gives_up_after_its_bounded_wait(cuda_device):
-    mine = torch.zeros(16, dtype=torch.int32, device=cuda_device)
-    peer = torch.zeros(16, dtype=torch.int32, device=cuda_device)
+    mine = torch.zeros(32, dtype=torch.int32, device=cuda_device)
+    peer = torch.zeros(32, dtype=torch.int32, device=cuda_device)
     t0 = time.perf_counter()
     _barrier([mine, peer], 0)  # nobody will ever write mine[1]
     torch.cuda.synchronize()
@@ -59,8 +59,8 @@ def test_a_reported_timeout_does_not_change_later_launches(cuda_device):
     """The status word is sticky until somebody reads it; prefill and decode launched while it still
     holds a late peer's time-out must compute exactly what they always compute."""
     dev = cuda_device
-    mine = torch.zeros(16, dtype=torch.int32, device=dev)
-    peer = torch.zeros(16, dtype=torch.int32, device=dev)
+    mine = torch.zeros(32, dtype=torch.int32, device=dev)
+    peer = torch.zeros(32, dtype=torch.int32, device=dev)
     _barrier([mine, peer], 0)  # times out; the word is NOT read afterwards
     pw = workloads.make_prefill("p", dev, lens_q=[200, 129], lens_k=[328, 129], num_heads=8, num_kv_heads=2,
                                 seed=77)
@@ -92,42 +92,43 @@ def _decode_with_fused_barrier(dev, w, outs, flags, rank):
 
 def test_barrier_folded_into_the_decode_call(cuda_device):
     """Two "ranks" whose buffers both live on this GPU: the call stores its rows into both output
-    buffers; its last kernel counts its CTAs off, signals and waits.  First with the peer's epochs
-    already published (passes at once, twice in a row: the CTA counter resets itself), then with a
-    peer that never arrives (bounded wait, status bit, rows still written, context usable)."""
+    buffers; every CTA of its last kernel reports to both ranks (2^20 per call and rank in all, in
+    slot 16 + rank) and one CTA waits for both.  First with the peer's reports already there (passes
+    at once, twice in a row), then with a peer that never reports (bounded wait, status bit, rows
+    still written, context usable)."""
     dev = cuda_device
     w = workloads.make_decode("d", dev, num_seqs=20, num_heads=8, num_kv_heads=2, ctx_kind="uniform",
                               ctx_lo=1, ctx_hi=2500, pool_blocks=4000, seed=79)
     ref = torch.empty_like(w.query)
     tch_cuda.paged_attention_v1(ref, w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale,
                                 w.block_tables, w.context_lens, 16, w.max_context_len, None)
-    mine = torch.zeros(16, dtype=torch.int32, device=dev)
-    peer = torch.zeros(16, dtype=torch.int32, device=dev)
-    mine[1] = 2
+    mine = torch.zeros(32, dtype=torch.int32, device=dev)
+    peer = torch.zeros(32, dtype=torch.int32, device=dev)
+    mine[17] = 2 << 20  # "rank 1" has already reported two calls in full
     for epoch in (1, 2):
         outs = [torch.full_like(w.query, float("nan")) for _ in range(2)]
         t0 = time.perf_counter()
         _decode_with_fused_barrier(dev, w, outs, [mine, peer], 0)
         torch.cuda.synchronize()
         assert time.perf_counter() - t0 < 0.5
-        assert int(peer[0]) == epoch and int(mine[0]) == epoch and int(mine[8]) == epoch and int(mine[9]) == 0
+        assert int(peer[16]) == epoch << 20 and int(mine[16]) == epoch << 20 and int(mine[10]) == epoch
         for o in outs:
             assert torch.equal(o.view(torch.int16), ref.view(torch.int16))
     assert _lib.last_status() == 0
     outs = [torch.full_like(w.query, float("nan")) for _ in range(2)]
     t0 = time.perf_counter()
-    _decode_with_fused_barrier(dev, w, outs, [mine, peer], 0)  # epoch 3: nobody writes mine[1] = 3
+    _decode_with_fused_barrier(dev, w, outs, [mine, peer], 0)  # call 3: nobody adds to mine[17]
     torch.cuda.synchronize()
     assert 0.2 < time.perf_counter() - t0 < 10.0
     assert _lib.last_status() == PEER_TIMEOUT
     for o in outs:
         assert torch.equal(o.view(torch.int16), ref.view(torch.int16))
-    assert int(mine[9]) == 0
+    assert int(mine[10]) == 3 and int(mine[16]) == 3 << 20
     assert float(torch.ones(8, device=dev).sum()) == 8.0
 
 
 def test_barrier_rejects_bad_arguments(cuda_device):
-    mine = torch.zeros(16, dtype=torch.int32, device=cuda_device)
+    mine = torch.zeros(32, dtype=torch.int32, device=cuda_device)
     with pytest.raises(_lib.AiciError, match="world must be 1..8"):
         _barrier([mine] * 9, 0)
     with pytest.raises(_lib.AiciError, match="rank inside it"):
