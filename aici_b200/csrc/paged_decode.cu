@@ -686,7 +686,10 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const Dec
     if (threadIdx.x < p.world) {
       const unsigned int lo = (unsigned int)(((uint64_t)blockIdx.x << 20) / gridDim.x);
       const unsigned int hi = (unsigned int)(((uint64_t)(blockIdx.x + 1) << 20) / gridDim.x);
-      __threadfence_system();  // cumulative: covers the stores of the whole CTA (ordered by the barrier above)
+      // release: the rows are performed at system scope before the add.  Cumulative: covers the
+      // stores of the whole CTA (ordered by the barrier above).  An acquire-release fence is enough
+      // for that; the sequentially consistent __threadfence_system() is not needed.
+      asm volatile("fence.acq_rel.sys;" ::: "memory");
       asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.peer_flags[threadIdx.x] + 16 + p.rank),
                    "r"(hi - lo)
                    : "memory");
