@@ -541,9 +541,13 @@ def run_ours(args):
         a_runs = [R.capture(lambda i=i: attention_only(i)).replay for i in range(n_graphs)]
     else:
         a_runs = [(lambda i=i: attention_only(i)) for i in range(n_graphs)]
+    a_group = None
+    if group is not None:
+        a_group = (R.capture(lambda: [attention_only(i) for i in range(spg)]).replay, spg)
+        a_group[0]()
     for i in range(3 * n_graphs):
         a_runs[i % n_graphs]()
-    att_ms = R.max_over_ranks(timed_steps(a_runs, args.steps)[0]) / args.steps
+    att_ms = R.max_over_ranks(timed_steps(a_runs, args.steps, group=a_group)[0]) / args.steps
     sampler.region(None)
     status = _lib.last_status()
     if status != 0:
