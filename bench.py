@@ -881,7 +881,7 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": config,
         "run": {
-            "launch": ("CUDA-graph replays, %d steps per graph" % spg) if use_graph else "eager launches",
+            "launch": ("CUDA-graph replays, %d step%s per graph" % (spg, "" if spg == 1 else "s")) if use_graph else "eager launches",
             "step_call": ("reshape_and_cache, then paged_attention_v1" if args.separate_calls else
                           "aici_decode_step (cache write and decode attention in one call, overlapped)"),
             "pool_copies": n_pools,
