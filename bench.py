@@ -52,7 +52,7 @@ MIN_STREAM_BYTES = 1 << 30
 # launch of rank 0's shard at each world size (`--profile decode --profile-world N`; world size 1:
 # the 16-sequence case of `--profile decode`; traffic grows in proportion to the tokens read).  The
 # summaries are under profiles/.  A world size without a capture reports no traffic figure.
-DECODE_TRAFFIC_RATIO = {1: 1.011, 2: 1.007, 4: 1.010, 8: 1.015}
+DECODE_TRAFFIC_RATIO = {1: 1.012, 2: 1.007, 4: 1.010, 8: 1.015}
 # DRAM bytes (read + write) of one full-size varlen_prefill_kernel launch (2 x 32768, 64/8 heads) on
 # one GPU: a one-pass ncu capture of `--profile prefill_full` (15.93 GB read, 1.18 GB written, for
 # 2.42 GB of q, k, v and output: the two sequences' K/V, 268 MB, do not fit the L2 and are fetched
