@@ -89,6 +89,8 @@ def test_large_batch_uses_the_plan_kernel(cuda_device):
     (8, 8, [16] * 40 + [5000] + [1] * 30),  # many one-tile rows around a long one
     (32, 8, [37] * 300),                  # more rows than warps: most spans hold several rows
     (8, 2, [0, 0, 0]),                    # nothing to read at all
+    (4, 4, [1100 + 13 * i for i in range(64)]),   # 256 rows of about five pieces: four warps merge a row
+    (4, 1, [600 + 7 * i for i in range(100)]),    # 400 rows of a few pieces: two warps merge a row
 ])
 def test_span_traversal_shapes(cuda_device, hq, hkv, ctx):
     """The default traversal gives each warp one span of consecutive tiles of the whole batch;
