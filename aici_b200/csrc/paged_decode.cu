@@ -561,28 +561,31 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const Dec
     for (int s0 = seq_first; s0 < seq; ++s0) c0 += s_pre[2 + s0 - seq_first];  // at most kRows - 1 terms
     tiles = active ? s_pre[2 + seq - seq_first] : 0;
   }
-  asm volatile("griddepcontrol.wait;" ::: "memory");  // no-op unless launched as a dependent grid
   int n = 0, pstride = 1;
   int64_t base = 0;
+  // spans mode: the partials of the row are `n` consecutive pieces from `base` on, `group` apart
+  auto locate = [&](int span) {
+    if (tiles <= 0) return;
+    const int kvh = head / p.group;
+    const int g0 = p.num_kv_heads * c0 + kvh * tiles;
+    const int first = g0 / span;
+    n = (g0 + tiles - 1) / span - first + 1;
+    base = (int64_t)(first + seq * p.num_kv_heads + kvh) * p.group + (head - kvh * p.group);
+    pstride = p.group;
+  };
+  if (kSpans && p.early_sums && active) {  // everything but the partials themselves is known before the wait
+    const int64_t n_items = (int64_t)total * p.num_kv_heads;
+    int span = (int)((n_items + p.decode_warps - 1) / p.decode_warps);
+    if (span < p.min_span) span = p.min_span;
+    locate(span);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // no-op unless launched as a dependent grid
   if (active) {
     if (kSpans) {
-      int span;
-      if (p.early_sums) {
-        const int64_t n_items = (int64_t)total * p.num_kv_heads;
-        span = (int)((n_items + p.decode_warps - 1) / p.decode_warps);
-        if (span < p.min_span) span = p.min_span;
-      } else {
+      if (!p.early_sums) {
         c0 = p.span_cum[seq];
         tiles = p.span_cum[seq + 1] - c0;
-        span = p.span_cum[p.num_seqs + 1];
-      }
-      if (tiles > 0) {
-        const int kvh = head / p.group;
-        const int g0 = p.num_kv_heads * c0 + kvh * tiles;
-        const int first = g0 / span;
-        n = (g0 + tiles - 1) / span - first + 1;
-        base = (int64_t)(first + seq * p.num_kv_heads + kvh) * p.group + (head - kvh * p.group);
-        pstride = p.group;
+        locate(p.span_cum[p.num_seqs + 1]);
       }
     } else {
       const int ctx = clamp_ctx(p, p.context_lens[seq]);
