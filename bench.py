@@ -11,7 +11,8 @@ layout) and the head outputs are gathered inside the step (stored into every ran
 attention call itself, or all-gathered over NCCL with --gather nccl), so the total work is fixed
 ("strong" scaling).  The metric is the achieved HBM traffic rate in TB/s computed from
 the ALGORITHMIC bytes of the step (K and V once per (sequence, kv head), q, out, block tables,
-context lengths, and the cache write), aggregated over all ranks.
+context lengths, and the cache write), aggregated over all ranks.  The timed steps are submitted
+as CUDA-graph replays, four steps to a graph (--steps-per-graph), each step one library call.
 
 The line also carries the long-context causal prefill throughput (2 x 32768 tokens, 64 q / 8 kv
 heads) in TFLOP/s under "prefill", the roofline of the dominant decode kernel, an end-to-end
